@@ -32,6 +32,7 @@ class PagedNeed:
     window: Optional[int] = None      # None: every past token stays visible
     v_head_dim: Optional[int] = None  # size of a value row when it differs from a key row's (None: head_dim)
     values_in_keys: bool = False      # a token's value is a part of its key row (a cache of latents): no value pool
+    chunk: Optional[int] = None       # a query sees only keys of its own block of ``chunk`` positions (counted from 0)
 
     @property
     def value_dim(self) -> int:
@@ -205,18 +206,24 @@ class CacheManager:
         return True
 
     def commit(self, req, n_new: int) -> None:
-        """n_new more tokens are in the cache; pages a window has passed go back."""
+        """n_new more tokens are in the cache; pages a window or a chunk mask has passed go back."""
         lv = self._live[req]
         lv.computed += n_new
         for g in self.groups:
             if len(g.tables[req]) < self.pages_for(lv.computed):
                 raise PageError(f"request {req!r}: {lv.computed} tokens committed but only "
                                 f"{len(g.tables[req])} pages reserved in group {g.index}")
-            w = g.need.window
-            if w is None:
+            w, c = g.need.window, g.need.chunk
+            if w is None and c is None:
                 continue
-            # the next query stands at position >= computed and sees keys >= computed - w + 1
-            first_needed = max(0, lv.computed - w + 1) // self.page_size
+            # the next query stands at position >= computed and sees keys >= computed - w + 1 (a window) and keys from
+            # the start of its own block on (a chunk mask); what lies before both is never read again
+            first_key = 0
+            if w is not None:
+                first_key = max(first_key, lv.computed - w + 1)
+            if c is not None:
+                first_key = max(first_key, (lv.computed // c) * c)
+            first_needed = first_key // self.page_size
             tab = g.tables[req]
             gone = []
             for p in range(lv.first_kept[g.index], min(first_needed, len(tab))):

@@ -5,7 +5,11 @@
 //   * a factor on the query that depends on its position only, given as a table q_scale[position]
 //     (a query "temperature" that grows with the context).
 // score(i, j) = (q_i . k_j) * scale * q_scale[i] + dist_bias[h][i - j] for j <= i (and j > i - window when a
-// window is set); softmax over the visible keys; out_i = out_scale * sum_j p_ij v_j.  Either table may be absent.
+// window is set, and j >= floor(i / chunk) * chunk when a chunk is set: block b is positions [b * chunk, (b + 1) * chunk)
+// of the request and a query sees only keys of its own block); softmax over the visible keys, with exp(sink[h])
+// added to the denominator when a sink is given (a scalar per head: in the online softmax it is the starting maximum
+// with weight 1 and a value row of zeros); out_i = out_scale * sum_j p_ij v_j.
+// Either table, the window, the chunk and the sink may be absent.
 // Scores, biases, softmax and the weighted sum are 32-bit (expf, not the fast intrinsic) for both cache dtypes.
 //
 // Four kernels (the fourth, `mma`, is described where it stands).  `simt`: one warp per (token, head), 32 keys at a time: any step, and the plain twin of the
@@ -42,7 +46,17 @@ struct BiasArgs {
     const float* q_scale;       // [n_pos] or null
     float scale, out_scale;
     int window;
+    int chunk;                  // > 0: keys before floor(p / chunk) * chunk are not seen
+    const float* sink;          // [H] or null: exp(sink[h]) joins the softmax denominator
 };
+
+// first key position that the query at position p sees
+__device__ __forceinline__ int first_visible(const BiasArgs& a, int p) {
+    int first = 0;
+    if (a.window > 0 && p - a.window + 1 > 0) first = p - a.window + 1;
+    if (a.chunk > 0) first = max(first, (p / a.chunk) * a.chunk);
+    return first;
+}
 
 // One warp walks the keys [k_lo, k_hi] (inclusive, absolute positions) of one (token, head) in chunks of 32 that
 // start at multiples of 32, and leaves the online-softmax state: acc (lane d holds dims d, d+32, ...), m, l.
@@ -113,13 +127,13 @@ attention_bias_simt_kernel(const T* q, long long q_stride, const T* k_pages, con
     for (int d = lane; d < dk; d += 32) qs[warp][d] = d < dkq ? to_f32(qrow[d]) : 0.f;     // key rows are padded with zeros
     __syncwarp();
     const float qf = a.scale * (a.q_scale ? a.q_scale[p] : 1.0f);
-    int first = 0;
-    if (a.window > 0 && p - a.window + 1 > 0) first = p - a.window + 1;
+    const int first = first_visible(a, p);
     constexpr int NACC = MAX_D / 32;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
+    if (a.sink) { m = a.sink[h]; l = 1.f; }
     warp_walk<T>(qs[warp], k_pages, v_pages, bt, p, h, hk, Hkv, dk, dv, page_size, first, p, a, qf, acc, m, l);
     T* orow = out + (size_t)t * out_stride + (size_t)h * dv;
     const float inv = a.out_scale / l;
@@ -167,8 +181,7 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
     const int h = h0 + wh;
     const bool live = wh < nh;
     const int seq = token_seq[t], p = positions[t];
-    int first = 0;
-    if (a.window > 0 && p - a.window + 1 > 0) first = p - a.window + 1;
+    const int first = first_visible(a, p);
     const int s_lo = max(first, split * SPLIT), s_hi = min(p, split * SPLIT + SPLIT - 1);
     if (s_lo > s_hi) {                                          // uniform over the CTA
         if (tid < nh) { const size_t pi = ((size_t)t * H + h0 + tid) * nsplit + split; part_ml[pi * 2] = -INFINITY; part_ml[pi * 2 + 1] = 0.f; }
@@ -313,7 +326,7 @@ template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_bias_merge_kernel(const float* part_o, const float* part_ml, const int* __restrict__ positions,
                             T* __restrict__ out, long long out_stride, int T_tokens, int H, int dv, int nsplit,
-                            float out_scale) {
+                            float out_scale, const float* __restrict__ sink) {
     pdl_wait();
     pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -322,10 +335,10 @@ attention_bias_merge_kernel(const float* part_o, const float* part_ml, const int
     const int t = (int)(gw / H), h = (int)(gw % H);
     const int used = min(nsplit, positions[t] / SPLIT + 1);
     const size_t base = ((size_t)t * H + h) * nsplit;
-    float mm = -INFINITY;
+    float mm = sink ? sink[h] : -INFINITY;
     for (int s = 0; s < used; ++s)
         if (part_ml[(base + s) * 2 + 1] > 0.f) mm = fmaxf(mm, part_ml[(base + s) * 2]);
-    float ll = 0.f;
+    float ll = sink ? expf(sink[h] - mm) : 0.f;              // the sink's term, taken before the splits'
     constexpr int NACC = MAX_D / 32;
     float acc[NACC];
 #pragma unroll
@@ -375,8 +388,7 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
     const int hk = h / (H / Hkv);
     const int* bt = block_table + (size_t)seq * bt_stride;
     const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;          // rows 2ty, 2ty+1; keys 4tx..4tx+3; dims tx + 8i
-    int first_key = 0;
-    if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
+    const int first_key = first_visible(a, pos0);           // of the tile's first row: later rows see no earlier key
     const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
 
     for (int i = tid; i < BQ * dk; i += THREADS) {
@@ -393,6 +405,7 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) { o[0][i] = 0.f; o[1][i] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    if (a.sink) { m_run[0] = m_run[1] = a.sink[h]; l_run[0] = l_run[1] = 1.f; }
     const int nd = (dv + 7) / 8;
     const int q0 = pos0 + 2 * ty;           // absolute position of this thread's first row
     constexpr int VEC = 16 / sizeof(T);
@@ -456,7 +469,7 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int kp = j * BK + 4 * tx + c;
-                const bool vis = kp <= qp && qp <= pos_max && (a.window <= 0 || kp > qp - a.window);
+                const bool vis = kp <= qp && qp <= pos_max && kp >= first_visible(a, qp);
                 float sc = s[r][c];
                 if (brow && vis) sc += Bs[qp - kp - dist0];
                 s[r][c] = vis ? sc : -INFINITY;
@@ -578,8 +591,7 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
     const int hk = h / (H / Hkv);
     const int* bt = block_table + (size_t)seq * bt_stride;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    int first_key = 0;
-    if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
+    const int first_key = first_visible(a, pos0);
     const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
     const int kp8 = dk / 8, vp8 = dv / 8;
 
@@ -643,6 +655,10 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
 #pragma unroll
     for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (a.sink) {                                                // in units of ln 2 like the scores; one thread of a row's quad carries its weight
+        m0 = m1 = a.sink[h] * LOG2E;
+        l0 = l1 = (lane & 3) == 0 ? 1.f : 0.f;
+    }
     const int nvt = dv / 8;
 
     for (int j = j_first; j <= j_last; ++j) {
@@ -671,7 +687,8 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
         // log2 e), so that the exponentials are exp2.  A tile that every row of the warp sees whole needs no mask.
         const int dist0 = pos0 - (j * MK + MK - 1);
         const int w_lo = pos0 + warp * 16, w_hi = w_lo + 15;
-        const bool whole = j * MK + MK - 1 <= w_lo && w_hi <= pos_max && (a.window <= 0 || j * MK > w_hi - a.window);
+        const bool whole = j * MK + MK - 1 <= w_lo && w_hi <= pos_max && (a.window <= 0 || j * MK > w_hi - a.window) &&
+                           (a.chunk <= 0 || j * MK >= (w_hi / a.chunk) * a.chunk);
         float mx0 = -INFINITY, mx1 = -INFINITY;
         if (whole) {
             const float* b0 = bs + (qp0 - j * MK - dist0) - 2 * (lane & 3);      // bias of (row r0, key j*MK + 2*(lane&3)); keys go down
@@ -692,7 +709,7 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
                 for (int e = 0; e < 4; ++e) {
                     const int kp = j * MK + n * 8 + 2 * (lane & 3) + (e & 1);
                     const int qp = (e < 2) ? qp0 : qp1;
-                    const bool vis = kp <= qp && qp <= pos_max && (a.window <= 0 || kp > qp - a.window);
+                    const bool vis = kp <= qp && qp <= pos_max && kp >= first_visible(a, qp);
                     float sc = s[n][e] * ((e < 2) ? qf0 : qf1);
                     if (brow && vis) sc += bs[qp - kp - dist0];
                     sc = vis ? sc : -INFINITY;
@@ -785,11 +802,13 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
                                     const int* tiles, int n_tiles, void* out, long long out_stride, float* part_o,
                                     float* part_ml, int nsplit, int T, int H, int Hkv, int dkq, int dk, int dv, int page_size,
                                     float scale, float out_scale, const float* dist_bias, int n_dist,
-                                    const float* q_scale, int window, int dtype, int impl, cudaStream_t stream) {
+                                    const float* q_scale, int window, int chunk, const float* sink, int dtype, int impl,
+                                    cudaStream_t stream) {
     if (T <= 0) return 0;
     if (int rc = check_sizes(H, Hkv, dk, dv, page_size, dtype)) return rc;
     if (dkq <= 0 || dkq > dk) return mllm_fail(1, "attention_bias: queries of %d against key rows of %d", dkq, dk);
-    BiasArgs a{dist_bias, n_dist, q_scale, scale, out_scale, window};
+    if (window < 0 || chunk < 0) return mllm_fail(1, "attention_bias: window %d, chunk %d", window, chunk);
+    BiasArgs a{dist_bias, n_dist, q_scale, scale, out_scale, window, chunk, sink};
     const long long warps = (long long)T * H;
     const long long blocks = (warps + WARPS - 1) / WARPS;
     if (blocks > 2147483647LL) return mllm_fail(1, "attention_bias: too many (token, head) pairs");
@@ -857,7 +876,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
                                   bt_stride, token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, NT, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (float*)out, out_stride, T, H, dv,
-                                  nsplit, out_scale));
+                                  nsplit, out_scale, a.sink));
         } else {
             if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(attention_bias_split_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MLLM_CUDA(mllm_launch(attention_bias_split_kernel<bf>, grid, block, smem, stream, true,
@@ -865,7 +884,7 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
                                   token_seq, positions, part_o, part_ml, H, Hkv, dkq, dk, dv, page_size, HG, KS, NT, a));
             MLLM_CUDA(mllm_launch(attention_bias_merge_kernel<bf>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, true,
                                   (const float*)part_o, (const float*)part_ml, positions, (bf*)out, out_stride, T, H, dv,
-                                  nsplit, out_scale));
+                                  nsplit, out_scale, a.sink));
         }
         return 0;
     }

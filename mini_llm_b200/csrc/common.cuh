@@ -11,7 +11,8 @@
 // dtype codes used across the C interface
 enum { MLLM_F32 = 0, MLLM_BF16 = 1 };
 // epilogue activation codes
-enum { MLLM_ACT_NONE = 0, MLLM_ACT_GELU_TANH = 1, MLLM_ACT_GELU_ERF = 2, MLLM_ACT_RELU = 3, MLLM_ACT_SILU = 4 };
+enum { MLLM_ACT_NONE = 0, MLLM_ACT_GELU_TANH = 1, MLLM_ACT_GELU_ERF = 2, MLLM_ACT_RELU = 3, MLLM_ACT_SILU = 4,
+       MLLM_ACT_SWIGLU_CLAMP = 5 };
 
 // Records a message for mllm_last_error() and returns the code.
 int mllm_fail(int code, const char* fmt, ...);
@@ -121,6 +122,20 @@ __device__ __forceinline__ float gelu_erf_f(float v) {
 __device__ __forceinline__ float gelu_tanh_fast(float v) {
     const float u = 0.7978845608f * (v + 0.044715f * v * v * v);
     return __fdividef(v, 1.0f + __expf(-2.0f * u));
+}
+// What a gated feed-forward makes of a gate value g and an up value u.  MLLM_ACT_SWIGLU_CLAMP: g is cut off above
+// `limit`, u on both sides; the result is g * sigmoid(alpha * g) * (u + 1).  Otherwise act(g) * u.
+__device__ __forceinline__ float gate_mul(float g, float u, int act, float limit, float alpha) {
+    if (act == MLLM_ACT_SWIGLU_CLAMP) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    if (act == MLLM_ACT_RELU) return fmaxf(g, 0.f) * u;
+    if (act == MLLM_ACT_SILU) return g / (1.0f + expf(-g)) * u;
+    if (act == MLLM_ACT_GELU_TANH) return gelu_tanh_f(g) * u;
+    if (act == MLLM_ACT_GELU_ERF) return gelu_erf_f(g) * u;
+    return g * u;
 }
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == MLLM_ACT_GELU_TANH) return gelu_tanh_f(v);

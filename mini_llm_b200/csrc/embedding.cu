@@ -7,29 +7,29 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const T* __restrict__ table, const T* __restrict__ pos_table,
-                             float* __restrict__ out, int D) {
+                             float* __restrict__ out, int D, int copies) {
     const int t = blockIdx.x;
     pdl_launch();               // the first kernel of a step: nothing before it to wait for
     const T* row = table + (size_t)ids[t] * D;
     const T* prow = pos_table ? pos_table + (size_t)pos[t] * D : nullptr;
-    float* o = out + (size_t)t * D;
+    float* o = out + (size_t)t * D * copies;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float v = to_f32(row[d]);
         if (prow) v += to_f32(prow[d]);
-        o[d] = v;
+        for (int c = 0; c < copies; ++c) o[(size_t)c * D + d] = v;     // a residual of several streams starts as copies
     }
 }
 
 MLLM_EXPORT int mllm_embed(const int* ids, const int* pos, const void* table, const void* pos_table,
-                           float* out, int T, int D, int dtype, cudaStream_t stream) {
+                           float* out, int T, int D, int copies, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (D <= 0) return mllm_fail(1, "embed: width %d", D);
+    if (D <= 0 || copies <= 0) return mllm_fail(1, "embed: width %d, %d copies", D, copies);
     int threads = D >= 256 ? 256 : ((D + 31) / 32) * 32;
     if (dtype == MLLM_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>(ids, pos, (const float*)table, (const float*)pos_table, out, D);
+        embed_kernel<float><<<T, threads, 0, stream>>>(ids, pos, (const float*)table, (const float*)pos_table, out, D, copies);
     else if (dtype == MLLM_BF16)
         embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(ids, pos, (const __nv_bfloat16*)table,
-                                                               (const __nv_bfloat16*)pos_table, out, D);
+                                                               (const __nv_bfloat16*)pos_table, out, D, copies);
     else
         return mllm_fail(1, "embed: unknown dtype code %d", dtype);
     MLLM_CHECK_LAUNCH("embed");

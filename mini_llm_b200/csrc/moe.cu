@@ -3,11 +3,13 @@
 //   moe_route       a warp per token: router logits in 32-bit, softmax over all experts, the best `keep` of `n_groups`
 //                   equal groups of neighbouring experts (a group's score is its largest), the `top` best experts inside
 //                   those groups (the lowest index wins among equals), weights = scores / (their sum + 1e-20).
+//                   With `bias` a number per expert is added to the logits first.  `mode` 1: no softmax over all
+//                   experts: the `top` largest logits are chosen and the weights are the softmax over those alone.
 //   moe_sort        one CTA: the (token, choice) pairs ordered by expert (a counting sort) and the experts' offsets;
 //                   with up to 16 tokens (decode steps) routing and ordering are one launch of one CTA.
 //   moe_grouped     out[row] = A[a_row] W_e^T for the pairs of expert e; a CTA finds its expert from the offsets on the
 //                   device, so the grid depends on the number of pairs only.  `gated`: W_e is [2F, K] (gate rows, then
-//                   up rows) and the result is silu(gate) * up.  Three kernels: CUDA cores, 32 pairs x 64 columns per
+//                   up rows) and the result is act(gate) * up (silu, or the clamped form of gate_mul).  Three kernels: CUDA cores, 32 pairs x 64 columns per
 //                   CTA (32-bit weights, odd sizes); tensor cores, 64 x 64 (bfloat16); and for up to 32 pairs (decode
 //                   steps) a CTA per pair and 64 columns whose warps stream the weight rows.
 //   moe_combine     y[t] (+)= sum_k weight[t][k] * pair_out[t * top + k], in the order of k.
@@ -22,8 +24,9 @@ constexpr int MOE_FEW_PAIRS = 32;     // up to this many (token, choice) pairs e
 
 // One warp routes one token; `s` is the warp's E floats of shared memory.
 template <typename T>
-__device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr, float* s, int D, int E, int top, int n_groups,
-                                            int keep, int* idx, float* wout, int lane) {
+__device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr, const float* __restrict__ bias, int mode,
+                                            float* s, int D, int E, int top, int n_groups, int keep, int* idx, float* wout,
+                                            int lane) {
     constexpr int V = 16 / sizeof(T);                           // elements per 16-byte load
     const bool vec = D % V == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)Wr % 16 == 0;
     for (int e0 = 0; e0 < E; e0 += 4) {                         // four experts at a time: their loads are in flight together
@@ -65,10 +68,30 @@ __device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const float v = warp_sum(a[u]);
-            if (lane == 0 && e0 + u < E) s[e0 + u] = v;
+            if (lane == 0 && e0 + u < E) s[e0 + u] = v + (bias ? bias[e0 + u] : 0.f);
         }
     }
     __syncwarp();
+    if (mode == 1) {
+        // the largest logits, and a softmax over them alone
+        if (lane == 0) {
+            float mx = -INFINITY, wsum = 0.f;
+            for (int k = 0; k < top; ++k) {
+                int best = 0;
+                float bv = -INFINITY;
+                for (int e = 0; e < E; ++e)
+                    if (s[e] > bv) { bv = s[e]; best = e; }
+                if (k == 0) mx = bv;
+                idx[k] = best;
+                wout[k] = expf(bv - mx);
+                wsum += wout[k];
+                s[best] = -INFINITY;                             // taken
+            }
+            for (int k = 0; k < top; ++k) wout[k] = wout[k] / wsum;
+        }
+        __syncwarp();
+        return;
+    }
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
     mx = warp_max(mx);
@@ -153,14 +176,15 @@ __device__ __forceinline__ void sort_pairs(const int* idx, int n, int E, int* of
 // 4 warps, a token each; dynamic shared memory: 4 * E floats
 template <typename T>
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int D, int E, int top, int n_groups, int keep,
-                 int* idx, float* wout) {
+moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, const float* __restrict__ bias, int mode, int Tn, int D,
+                 int E, int top, int n_groups, int keep, int* idx, float* wout) {
     extern __shared__ float sc[];
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= Tn) return;
-    route_token(h + (size_t)t * ld, Wr, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top, wout + (size_t)t * top, lane);
+    route_token(h + (size_t)t * ld, Wr, bias, mode, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top,
+                wout + (size_t)t * top, lane);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -174,14 +198,14 @@ moe_sort_kernel(const int* idx, int n, int E, int* offsets, int* sorted) {
 // dynamic shared memory: 8 * E floats, then E + 1 ints
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_route_sort_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn, int D, int E, int top, int n_groups,
-                      int keep, int* idx, float* wout, int* offsets, int* sorted) {
+moe_route_sort_kernel(const T* h, long long ld, const T* __restrict__ Wr, const float* __restrict__ bias, int mode, int Tn,
+                      int D, int E, int top, int n_groups, int keep, int* idx, float* wout, int* offsets, int* sorted) {
     extern __shared__ float sc[];
     int* cnt = reinterpret_cast<int*>(sc + 8 * E);
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = warp; t < Tn; t += 8)
-        route_token(h + (size_t)t * ld, Wr, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top,
+        route_token(h + (size_t)t * ld, Wr, bias, mode, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top,
                     wout + (size_t)t * top, lane);
     __syncthreads();                                         // the CTA's own writes of idx are visible to all its threads
     sort_pairs(idx, Tn * top, E, offsets, sorted, cnt);
@@ -190,7 +214,7 @@ moe_route_sort_kernel(const T* h, long long ld, const T* __restrict__ Wr, int Tn
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, long long ldo, const int* offsets,
-                   const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated) {
+                   const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated, float limit, float alpha) {
     __shared__ float As[32][33];
     __shared__ float Ws[64][33];
     __shared__ float Us[64][33];
@@ -263,7 +287,7 @@ moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out
             const int n = n0 + tx + 16 * i;
             if (n >= N) continue;
             float v = acc[j][i];
-            if (gated) v = v / (1.0f + expf(-v)) * acu[j][i];
+            if (gated) v = gate_mul(v, acu[j][i], gated, limit, alpha);
             out[(size_t)rows_o[r] * ldo + n] = from_f32<TO>(v);
         }
     }
@@ -276,7 +300,7 @@ moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, long long ldo, const int* offsets,
-                const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated) {
+                const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated, float limit, float alpha) {
     extern __shared__ float xs[];                                // [K]
     __shared__ int s_e;
     pdl_wait();
@@ -334,7 +358,7 @@ moe_rows_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, l
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = warp_sum(acc[u]);
-        if (gated) v = v / (1.0f + expf(-v)) * warp_sum(acu[u]);
+        if (gated) v = gate_mul(v, warp_sum(acu[u]), gated, limit, alpha);
         if (lane == 0 && n0 + u < N) out[orow + n0 + u] = from_f32<TO>(v);
     }
 }
@@ -366,7 +390,8 @@ __device__ __forceinline__ void g_cp16(void* dst, const void* src, bool valid) {
 template <typename TO, int GATED>
 __global__ void __launch_bounds__(128)
 moe_grouped_mma_kernel(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* __restrict__ W, TO* out, long long ldo,
-                       const int* offsets, const int* sorted, int E, int N, int K, int a_div, int out_by_pair) {
+                       const int* offsets, const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int act,
+                       float limit, float alpha) {
     using bf = __nv_bfloat16;
     extern __shared__ __align__(16) unsigned char gsm[];
     constexpr int STAGE = (GM + GN * (1 + GATED)) * GROW;        // elements per stage
@@ -451,7 +476,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* A, long long lda, const __nv_bfloat1
             const int r = r0 + (c >> 1) * 8, col = n0 + n * 8 + 2 * (lane & 3) + (c & 1);
             if (r < cnt && col < N) {
                 float v = acc[n][c];
-                if (GATED) v = v / (1.0f + expf(-v)) * acu[n][c];
+                if (GATED) v = gate_mul(v, acu[n][c], act, limit, alpha);
                 out[(size_t)rows_o[r] * ldo + col] = from_f32<TO>(v);
             }
         }
@@ -474,9 +499,12 @@ moe_combine_kernel(const float* pair_out, const float* w, float* y, long long ld
 
 MLLM_EXPORT int mllm_moe_max_experts() { return MAX_E; }
 
-MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, int Tn, int D, int E, int top, int n_groups,
-                               int keep, int* idx, float* w, int* offsets, int* sorted, int dtype, cudaStream_t stream) {
+MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, const float* bias, int mode, int Tn, int D, int E,
+                               int top, int n_groups, int keep, int* idx, float* w, int* offsets, int* sorted, int dtype,
+                               cudaStream_t stream) {
     if (Tn <= 0) return 0;
+    if (mode != 0 && mode != 1) return mllm_fail(1, "moe_route: unknown mode %d", mode);
+    if (mode == 1 && n_groups != 1) return mllm_fail(1, "moe_route: the softmax over the chosen logits takes no groups");
     if (E < 1 || E > MAX_E || top < 1 || top > E) return mllm_fail(1, "moe_route: %d experts (at most %d), top %d", E, MAX_E, top);
     if (n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || n_groups > 64)
         return mllm_fail(1, "moe_route: %d experts in %d groups (at most 64), %d kept", E, n_groups, keep);
@@ -485,11 +513,11 @@ MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, int 
         const size_t smem = (size_t)8 * E * 4 + (size_t)(E + 1) * 4;
         if (dtype == MLLM_F32)
             MLLM_CUDA(mllm_launch(moe_route_sort_kernel<float>, dim3(1), dim3(256), smem, stream, true, (const float*)h, ld,
-                                  (const float*)Wr, Tn, D, E, top, n_groups, keep, idx, w, offsets, sorted));
+                                  (const float*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, idx, w, offsets, sorted));
         else if (dtype == MLLM_BF16)
             MLLM_CUDA(mllm_launch(moe_route_sort_kernel<__nv_bfloat16>, dim3(1), dim3(256), smem, stream, true,
-                                  (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, Tn, D, E, top, n_groups, keep, idx, w,
-                                  offsets, sorted));
+                                  (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, bias, mode, Tn, D, E, top, n_groups, keep,
+                                  idx, w, offsets, sorted));
         else
             return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
         return 0;
@@ -497,10 +525,10 @@ MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, int 
     const size_t smem = (size_t)4 * E * 4;
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(moe_route_kernel<float>, dim3((Tn + 3) / 4), dim3(128), smem, stream, true, (const float*)h, ld,
-                              (const float*)Wr, Tn, D, E, top, n_groups, keep, idx, w));
+                              (const float*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, idx, w));
     else if (dtype == MLLM_BF16)
         MLLM_CUDA(mllm_launch(moe_route_kernel<__nv_bfloat16>, dim3((Tn + 3) / 4), dim3(128), smem, stream, true,
-                              (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, Tn, D, E, top, n_groups, keep, idx, w));
+                              (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, idx, w));
     else
         return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
     MLLM_CUDA(mllm_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, true, (const int*)idx, Tn * top, E, offsets, sorted));
@@ -509,15 +537,17 @@ MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, int 
 
 MLLM_EXPORT int mllm_moe_few_tokens() { return MOE_FEW_TOKENS; }
 
-// kind 0: A in `dtype`, gated, out in `dtype` (the experts' first product with its activation);
+// kind 0: A in `dtype`, gated, out in `dtype` (the experts' first product with its activation `act`: MLLM_ACT_SILU, or
+// MLLM_ACT_SWIGLU_CLAMP with `limit` and `alpha`);
 // kind 1: A in `dtype`, out 32-bit (the experts' second product).
 MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, const int* offsets,
                                  const int* sorted, int n_pairs, int E, int N, int K, int a_div, int out_by_pair, int kind,
-                                 int dtype, cudaStream_t stream) {
+                                 int act, float limit, float alpha, int dtype, cudaStream_t stream) {
     if (n_pairs <= 0 || N <= 0) return 0;
     const dim3 grid((n_pairs + 31) / 32 + E, (N + 63) / 64), block(256);
     if (grid.y > 65535) return mllm_fail(1, "moe_grouped: too many columns");
-    const int gated = kind == 0;
+    if (kind == 0 && act != MLLM_ACT_SILU && act != MLLM_ACT_SWIGLU_CLAMP) return mllm_fail(1, "moe_grouped: activation code %d", act);
+    const int gated = kind == 0 ? act : 0;
     if (n_pairs <= MOE_FEW_PAIRS && (size_t)K * 4 <= 96 * 1024) {
         const dim3 fg(n_pairs, (N + 63) / 64);
         const size_t smem = (size_t)K * 4;
@@ -529,7 +559,7 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
                 raised = true;                                                                                           \
             }                                                                                                            \
             MLLM_CUDA(mllm_launch(moe_rows_kernel<TA, TW, TO>, fg, block, smem, stream, true, (const TA*)A, lda, (const TW*)W, \
-                                  (TO*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated));                  \
+                                  (TO*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated, limit, alpha));    \
         } while (0)
         if (dtype == MLLM_F32) MLLM_ROWS(float, float, float);
         else if (dtype == MLLM_BF16 && kind == 0) MLLM_ROWS(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
@@ -548,25 +578,26 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
                 raised = true;
             }
             MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<__nv_bfloat16, 1>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A,
-                                  lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair));
+                                  lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, act, limit,
+                                  alpha));
         } else {
             constexpr size_t smem = (size_t)2 * (GM + GN) * GROW * 2;
             MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<float, 0>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A, lda,
-                                  (const __nv_bfloat16*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair));
+                                  (const __nv_bfloat16*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, 0, 0.f, 0.f));
         }
         return 0;
     }
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<float, float, float>, grid, block, 0, stream, true, (const float*)A, lda,
-                              (const float*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated));
+                              (const float*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated, limit, alpha));
     else if (dtype == MLLM_BF16 && kind == 0)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, true,
                               (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E,
-                              N, K, a_div, out_by_pair, gated));
+                              N, K, a_div, out_by_pair, gated, limit, alpha));
     else if (dtype == MLLM_BF16)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, block, 0, stream, true,
                               (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (float*)out, ldo, offsets, sorted, E, N, K,
-                              a_div, out_by_pair, gated));
+                              a_div, out_by_pair, gated, limit, alpha));
     else
         return mllm_fail(1, "moe_grouped: unknown dtype code %d", dtype);
     return 0;

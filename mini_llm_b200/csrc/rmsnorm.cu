@@ -106,18 +106,15 @@ int launch(const float* x, long long x_stride, const int* rows, const float* w1,
 // out[t][c] = act(gu[t][c]) * gu[t][F + c]: the gate and the up half of one product's output.
 template <typename T>
 __global__ void __launch_bounds__(256)
-gated_act_kernel(const T* gu, long long gu_stride, T* __restrict__ out, long long out_stride, int rows, int F, int act) {
+gated_act_kernel(const T* gu, long long gu_stride, T* __restrict__ out, long long out_stride, int rows, int F, int act,
+                 float limit, float alpha) {
     pdl_wait();
     pdl_launch();
     const long long total = (long long)rows * F;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / F), c = (int)(i % F);
         const float g = to_f32(gu[(size_t)t * gu_stride + c]), u = to_f32(gu[(size_t)t * gu_stride + F + c]);
-        float a;
-        if (act == MLLM_ACT_RELU) a = fmaxf(g, 0.f);
-        else if (act == MLLM_ACT_SILU) a = g / (1.0f + expf(-g));
-        else a = apply_act(g, act);
-        out[(size_t)t * out_stride + c] = from_f32<T>(a * u);
+        out[(size_t)t * out_stride + c] = from_f32<T>(gate_mul(g, u, act, limit, alpha));
     }
 }
 
@@ -201,16 +198,16 @@ MLLM_EXPORT int mllm_rmsnorm(const float* x, long long x_stride, const int* rows
 }
 
 MLLM_EXPORT int mllm_gated_act(const void* gu, long long gu_stride, void* out, long long out_stride, int rows, int F,
-                               int act, int dtype, cudaStream_t stream) {
+                               int act, float limit, float alpha, int dtype, cudaStream_t stream) {
     if (rows <= 0 || F <= 0) return 0;
     const long long total = (long long)rows * F;
     const int grid = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)gu, gu_stride,
-                              (float*)out, out_stride, rows, F, act));
+                              (float*)out, out_stride, rows, F, act, limit, alpha));
     else if (dtype == MLLM_BF16)
         MLLM_CUDA(mllm_launch(gated_act_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
-                              (const __nv_bfloat16*)gu, gu_stride, (__nv_bfloat16*)out, out_stride, rows, F, act));
+                              (const __nv_bfloat16*)gu, gu_stride, (__nv_bfloat16*)out, out_stride, rows, F, act, limit, alpha));
     else
         return mllm_fail(1, "gated_act: unknown dtype code %d", dtype);
     return 0;

@@ -183,3 +183,28 @@ MLLM_EXPORT int mllm_sample(const float* logits, long long ld, int R, int V, con
                           uniform, out));
     return 0;
 }
+
+// A cap on the logits: x <- cap * tanh(x / cap), in place, 32-bit (tanhf).  It keeps the order of a row's entries, so
+// the argmax is unchanged; sampled tokens and the logits that are handed out need the values.
+namespace {
+__global__ void __launch_bounds__(256)
+softcap_kernel(float* logits, long long ld, int R, int V, float cap) {
+    pdl_wait();
+    pdl_launch();
+    const long long total = (long long)R * V;
+    const float inv = 1.0f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float* p = logits + (size_t)(i / V) * ld + (i % V);
+        *p = cap * tanhf(*p * inv);
+    }
+}
+}  // namespace
+
+MLLM_EXPORT int mllm_softcap(float* logits, long long ld, int R, int V, float cap, cudaStream_t stream) {
+    if (R <= 0 || V <= 0) return 0;
+    if (!(cap > 0.f)) return mllm_fail(1, "softcap: the cap must be positive");
+    const long long total = (long long)R * V;
+    const int grid = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    MLLM_CUDA(mllm_launch(softcap_kernel, dim3(grid), dim3(256), 0, stream, true, logits, ld, R, V, cap));
+    return 0;
+}

@@ -24,7 +24,7 @@ DECODE_CLUSTER_SPLITS = 8    # splits that can meet in one thread-block cluster 
 _FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}      # what the products' epilogues take
-_GATE_ACT = {"gelu_tanh": 1, "gelu_erf": 2, "relu": 3, "silu": 4}   # what gated_act takes
+_GATE_ACT = {"gelu_tanh": 1, "gelu_erf": 2, "relu": 3, "silu": 4, "swiglu_clamp": 5}   # what gated_act takes
 _lib = None
 
 c_int, c_ll, c_float, c_void_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
@@ -40,7 +40,7 @@ def _signatures(lib):
     lib.mllm_set_pdl.argtypes = [c_int]
     lib.mllm_set_pdl.restype = c_int
     sig = {
-        "mllm_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mllm_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_resolve_tokens": [c_void_p, c_int, c_void_p, c_int, c_void_p],
         "mllm_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_kv_write": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -90,14 +90,21 @@ def _signatures(lib):
         "mllm_gated_recurrence_wide": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p],
-        "mllm_gated_act": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_gated_act": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
         "mllm_paged_write": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_paged_write_kv": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p],
         "mllm_attention_bias_split_keys": [],
         "mllm_attention_bias": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+                                c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+        "mllm_qk_norm_rope": [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                              c_void_p, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                              c_int, c_int, c_void_p],
+        "mllm_hyper_step": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                            c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_hyper_max_streams": [],
+        "mllm_softcap": [c_void_p, c_ll, c_int, c_int, c_float, c_void_p],
         "mllm_gated_recurrence": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                   c_int, c_void_p],
@@ -118,10 +125,10 @@ def _signatures(lib):
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_gated_group_norm": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int,
                                   c_void_p],
-        "mllm_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                           c_void_p, c_int, c_void_p],
+        "mllm_moe_route": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_moe_grouped": [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_int, c_void_p],
+                             c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
         "mllm_moe_combine": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_argmax_sliced": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -315,12 +322,16 @@ def _rows(name: str, t: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- embedding
-def embed(ids, positions, table, pos_table, out) -> None:
-    """out[t] = table[ids[t]] (+ pos_table[positions[t]]), 32-bit."""
+def embed(ids, positions, table, pos_table, out, copies: int = 1) -> None:
+    """out[t] = table[ids[t]] (+ pos_table[positions[t]]), 32-bit; with ``copies`` > 1 a row of out holds that many
+    copies of the token's row side by side (a residual of several streams at its start)."""
     _cuda("ids", ids, torch.int32)
     _cuda("table", table)
     _cuda("out", out, torch.float32)
     T, D = out.shape
+    if copies < 1 or D % copies:
+        raise KernelError(f"embed: {copies} copies in rows of {D}")
+    D //= copies
     if ids.numel() != T or table.shape[1] != D:
         raise KernelError(f"embed: {ids.numel()} ids, table {tuple(table.shape)}, out {tuple(out.shape)}")
     pp = None
@@ -331,7 +342,7 @@ def embed(ids, positions, table, pos_table, out) -> None:
             raise KernelError("embed: position table or positions do not fit")
         pp = pos_table.data_ptr()
     _call("mllm_embed", ids.data_ptr(), positions.data_ptr() if pos_table is not None else None,
-          table.data_ptr(), pp, out.data_ptr(), T, D, _dt(table), _stream())
+          table.data_ptr(), pp, out.data_ptr(), T, D, int(copies), _dt(table), _stream())
 
 
 def resolve_tokens(ids, sampled) -> None:
@@ -397,8 +408,10 @@ def rmsnorm(x, weight, eps: float, out, rows=None, unit_offset: bool = True, wei
           float(scale), _dt(out), _stream())
 
 
-def gated_act(gu, out, act: str) -> None:
-    """out[t, c] = act(gu[t, c]) * gu[t, F + c] for gu [T, 2F]: the gate and the up half of one product."""
+def gated_act(gu, out, act: str, limit: float = 0.0, alpha: float = 1.0) -> None:
+    """out[t, c] = act(gu[t, c]) * gu[t, F + c] for gu [T, 2F]: the gate and the up half of one product.
+    ``act`` "swiglu_clamp": with g the gate cut off above ``limit`` and u the up value cut off at +-``limit``,
+    out = g * sigmoid(alpha * g) * (u + 1)."""
     _cuda("gu", gu, contiguous=False)
     _cuda("out", out, gu.dtype, contiguous=False)
     T, F = out.shape
@@ -406,8 +419,10 @@ def gated_act(gu, out, act: str) -> None:
         raise KernelError(f"gated_act: gu {tuple(gu.shape)} against out {tuple(out.shape)}")
     if act not in _GATE_ACT:
         raise KernelError(f"gated_act: unknown activation {act!r}; known: {sorted(_GATE_ACT)}")
+    if act == "swiglu_clamp" and not limit > 0:
+        raise KernelError("gated_act: the clamped form needs a positive limit")
     _call("mllm_gated_act", gu.data_ptr(), _rows("gu", gu), out.data_ptr(), _rows("out", out), T, F, _GATE_ACT[act],
-          _dt(gu), _stream())
+          float(limit), float(alpha), _dt(gu), _stream())
 
 
 # --------------------------------------------------------------------------- linear
@@ -779,10 +794,14 @@ _bias_split_keys = None
 
 
 def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, num_kv_heads, scale, dist_bias=None,
-                     q_scale=None, out_scale: float = 1.0, window=None, impl: Optional[str] = None) -> None:
+                     q_scale=None, out_scale: float = 1.0, window=None, chunk=None, sink=None,
+                     impl: Optional[str] = None) -> None:
     """Causal attention over the cache with keys and values of different sizes, an additive score bias
     ``dist_bias[head, i - j]`` (float32 [heads, n]) and a factor ``q_scale[position]`` (float32 [n]) on the query:
     out[t] = out_scale * softmax_j((q_t . k_j) * scale * q_scale[p_t] + dist_bias[h, p_t - j]) v_j.
+    ``window``: only the last ``window`` keys are seen; ``chunk``: only keys from floor(p_t / chunk) * chunk on (block b is
+    positions [b * chunk, (b + 1) * chunk) of the request); ``sink`` (float32 [heads]): exp(sink[h]) is one more
+    term of the softmax's denominator and of nothing else.
 
     q [T, heads * dkq], k_pages [P, kv_heads, page_size, dk] with dk >= dkq a multiple of 8 (key rows padded with
     zeros), v_pages [P, kv_heads, page_size, dv], out [T, heads * dv] (rows contiguous; a column slice of a wider
@@ -817,6 +836,10 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
         _cuda("q_scale", q_scale, torch.float32)
         if ctx.max_ctx_len > q_scale.numel():
             raise KernelError("biased_attention: a position exceeds the query-scale table")
+    if sink is not None:
+        _cuda("sink", sink, torch.float32)
+        if sink.numel() != num_heads:
+            raise KernelError("biased_attention: one sink per query head")
     if impl is None:
         impl = "simt"
         if getattr(ctx, "decode_only", False):
@@ -848,12 +871,118 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
           _rows("block_table", block_table), ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), tiles, n_tiles,
           out.data_ptr(), ldo, part_o, part_ml, nsplit, T, num_heads, num_kv_heads, dkq, dk, dv, ps, float(scale),
           float(out_scale), dist_bias.data_ptr() if dist_bias is not None else None, n_dist,
-          q_scale.data_ptr() if q_scale is not None else None, int(window or 0), _dt(q),
-          {"simt": 0, "tiled": 1, "split": 2, "mma": 3}[impl], _stream())
+          q_scale.data_ptr() if q_scale is not None else None, int(window or 0), int(chunk or 0),
+          sink.data_ptr() if sink is not None else None, _dt(q), {"simt": 0, "tiled": 1, "split": 2, "mma": 3}[impl],
+          _stream())
     if impl == "split":
         global launches
         launches += 1           # the kernel that merges the splits
 
+
+
+# --------------------------------------------------------------------------- normed and rotated queries and keys
+def qk_norm_rope(proj, q_off: int, k_off: int, v_off: int, ctx, q_out, k_pages, v_pages, slot_mapping, *, heads: int,
+                 kv_heads: int, head_dim: int, v_head_dim: int, q_norm=None, k_norm=None, eps: float = 0.0, freq=None,
+                 rot_dims: int = 0, interleaved: bool = True) -> None:
+    """What stands between a Q | K | V projection and attention when queries and keys are normed and rotated.
+
+    proj [T, .] holds a token's queries at column q_off (heads * head_dim), keys at k_off (kv_heads * head_dim) and
+    values at v_off (kv_heads * v_head_dim).  ``q_norm`` / ``k_norm`` (float32, one weight per column of the WHOLE
+    projection, or None): x / sqrt(mean(x^2) + eps) * w over all heads of the token at once.  Then the first
+    ``rot_dims`` entries of every head turn by position * freq[i] (float32 [rot_dims / 2]); ``interleaved``: entry 2i
+    pairs with 2i + 1, else i with i + rot_dims / 2.  Queries go to q_out [T, heads * head_dim]; keys (rows of the
+    pages may be padded) and values go to the tokens' slots (``slot_mapping`` None: nothing is cached).  All 32-bit
+    up to the final rounding."""
+    _cuda("proj", proj, contiguous=False)
+    _cuda("q_out", q_out, proj.dtype, contiguous=False)
+    T = proj.shape[0]
+    ld = _rows("proj", proj)
+    nq, nk, nv = heads * head_dim, kv_heads * head_dim, kv_heads * v_head_dim
+    if max(q_off + nq, k_off + nk, v_off + nv) > proj.shape[1] or tuple(q_out.shape) != (T, nq):
+        raise KernelError(f"qk_norm_rope: proj {tuple(proj.shape)} against {nq} + {nk} + {nv} columns, q_out {tuple(q_out.shape)}")
+    for name, w, n in (("q_norm", q_norm, nq), ("k_norm", k_norm, nk)):
+        if w is not None:
+            _cuda(name, w, torch.float32)
+            if w.numel() != n:
+                raise KernelError(f"qk_norm_rope: {name} has {w.numel()} weights for {n} columns")
+    if rot_dims:
+        _cuda("freq", freq, torch.float32)
+        if rot_dims % 2 or rot_dims > head_dim or freq.numel() != rot_dims // 2:
+            raise KernelError(f"qk_norm_rope: {rot_dims} rotated entries of {head_dim}, {freq.numel()} frequencies")
+    dkp, ps = head_dim, 1
+    if slot_mapping is not None:
+        _cuda("k_pages", k_pages, proj.dtype)
+        _cuda("v_pages", v_pages, proj.dtype)
+        _cuda("slot_mapping", slot_mapping, torch.int32)
+        _, G, ps, dkp = k_pages.shape
+        if G != kv_heads or dkp < head_dim or v_pages.shape[3] != v_head_dim or v_pages.shape[:3] != k_pages.shape[:3] \
+                or slot_mapping.numel() != T:
+            raise KernelError(f"qk_norm_rope: pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit")
+    _call("mllm_qk_norm_rope", proj.data_ptr(), ld, int(q_off), int(k_off), int(v_off), int(heads), int(kv_heads),
+          int(head_dim), int(v_head_dim), q_norm.data_ptr() if q_norm is not None else None,
+          k_norm.data_ptr() if k_norm is not None else None, float(eps), freq.data_ptr() if rot_dims else None,
+          int(rot_dims), int(bool(interleaved)), ctx.positions.data_ptr(), q_out.data_ptr(), _rows("q_out", q_out),
+          k_pages.data_ptr() if slot_mapping is not None else None, v_pages.data_ptr() if slot_mapping is not None else None,
+          int(dkp), slot_mapping.data_ptr() if slot_mapping is not None else None, int(ps), T, _dt(proj), _stream())
+
+
+# --------------------------------------------------------------------------- a residual of several streams
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_step(x, streams: int, *, y=None, mix=None, out_weights=None, in_weights=None, gamma=None, beta=None, eps: float = 0.0,
+               rows=None, h=None, sum_out=None) -> None:
+    """One pass over a residual of ``streams`` streams, x [T, streams * D] (32-bit, changed in place).
+
+    With ``y`` [T, D] (32-bit; the result of the sublayer that has just run), ``mix`` [streams, streams] ([from, to])
+    and ``out_weights`` [streams]: x_t <- sum_s mix[s, t] x_s + out_weights[t] * y, all streams at once from the old
+    ones.  With ``h`` [R, D] (activation dtype) and ``gamma``: h = norm(sum_s in_weights[s] x_s) of the new streams
+    (``in_weights`` None: the plain sum); LayerNorm with ``beta``, an RMS norm without.  ``sum_out`` [R, D] (32-bit)
+    gets the read before its norm.  ``rows`` (int32 [R]) gathers the rows that are read (no write then)."""
+    _cuda("x", x, torch.float32)
+    T = x.shape[0]
+    if streams < 1 or streams > HYPER_MAX_STREAMS or x.shape[1] % streams:
+        raise KernelError(f"hyper_step: {streams} streams (at most {HYPER_MAX_STREAMS}) in rows of {x.shape[1]}")
+    D = x.shape[1] // streams
+    R = T if rows is None else rows.numel()
+    if y is not None:
+        _cuda("y", y, torch.float32, contiguous=False)
+        _cuda("mix", mix, torch.float32)
+        _cuda("out_weights", out_weights, torch.float32)
+        if tuple(y.shape) != (T, D) or mix.numel() != streams * streams or out_weights.numel() != streams or rows is not None:
+            raise KernelError("hyper_step: y, mix or out_weights do not fit the streams")
+    if rows is not None:
+        _cuda("rows", rows, torch.int32)
+    if in_weights is not None:
+        _cuda("in_weights", in_weights, torch.float32)
+        if in_weights.numel() != streams:
+            raise KernelError("hyper_step: one read weight per stream")
+    dt = F32
+    if h is not None:
+        _cuda("h", h, contiguous=False)
+        _cuda("gamma", gamma, torch.float32)
+        if tuple(h.shape) != (R, D) or gamma.numel() != D or (beta is not None and beta.numel() != D):
+            raise KernelError(f"hyper_step: h {tuple(h.shape)} against {R} rows of {D}")
+        if beta is not None:
+            _cuda("beta", beta, torch.float32)
+        dt = _dt(h)
+    if sum_out is not None:
+        _cuda("sum_out", sum_out, torch.float32)
+        if tuple(sum_out.shape) != (R, D):
+            raise KernelError("hyper_step: sum_out does not fit")
+    _call("mllm_hyper_step", x.data_ptr(), y.data_ptr() if y is not None else None, _rows("y", y) if y is not None else 0,
+          mix.data_ptr() if y is not None else None, out_weights.data_ptr() if y is not None else None,
+          in_weights.data_ptr() if in_weights is not None else None, gamma.data_ptr() if h is not None else None,
+          beta.data_ptr() if (h is not None and beta is not None) else None, float(eps),
+          rows.data_ptr() if rows is not None else None, h.data_ptr() if h is not None else None,
+          _rows("h", h) if h is not None else 0, sum_out.data_ptr() if sum_out is not None else None, R, int(streams), D, dt,
+          _stream())
+
+
+def softcap(logits, cap: float) -> None:
+    """In place on 32-bit logits [R, V]: x <- cap * tanh(x / cap)."""
+    _cuda("logits", logits, torch.float32, contiguous=False)
+    _call("mllm_softcap", logits.data_ptr(), _rows("logits", logits), logits.shape[0], logits.shape[1], float(cap), _stream())
 
 
 # --------------------------------------------------------------------------- joining a branch's result to the residual
@@ -1075,11 +1204,13 @@ MOE_MAX_EXPERTS = 512
 _moe_few_tokens = None
 
 
-def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int = 1, keep: int = 1) -> None:
+def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int = 1, keep: int = 1, bias=None,
+              mode: str = "softmax_all") -> None:
     """Per row of h: softmax of the router's logits (32-bit) over all experts; the best ``keep`` of ``groups`` equal
     groups of neighbours (by their largest score); the ``top`` best experts within them -> idx [T, top] (int32) and
-    weights [T, top] (scores over their sum + 1e-20).  Then the (row, choice) pairs ordered by expert:
-    offsets [E + 1], order [T * top]."""
+    weights [T, top] (scores over their sum + 1e-20).  ``bias`` (float32 [E]) is added to the logits first.  ``mode``
+    "softmax_top": the ``top`` largest logits are chosen and weighted by the softmax over those alone (no groups).
+    Then the (row, choice) pairs ordered by expert: offsets [E + 1], order [T * top]."""
     _cuda("h", h, contiguous=False)
     _cuda("router", router, h.dtype)
     for name, t, dt in (("idx", idx, torch.int32), ("weights", weights, torch.float32), ("offsets", offsets, torch.int32),
@@ -1090,7 +1221,14 @@ def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int 
     if router.shape[1] != D or idx.numel() != T * top or weights.numel() != T * top or offsets.numel() != E + 1 \
             or order.numel() != T * top:
         raise KernelError("moe_route: shapes do not fit")
-    _call("mllm_moe_route", h.data_ptr(), _rows("h", h), router.data_ptr(), T, D, E, int(top), int(groups), int(keep),
+    if bias is not None:
+        _cuda("bias", bias, torch.float32)
+        if bias.numel() != E:
+            raise KernelError("moe_route: one bias per expert")
+    if mode not in ("softmax_all", "softmax_top"):
+        raise KernelError(f"moe_route: unknown mode {mode!r}")
+    _call("mllm_moe_route", h.data_ptr(), _rows("h", h), router.data_ptr(), bias.data_ptr() if bias is not None else None,
+          int(mode == "softmax_top"), T, D, E, int(top), int(groups), int(keep),
           idx.data_ptr(), weights.data_ptr(), offsets.data_ptr(), order.data_ptr(), _dt(h), _stream())
     global launches, _moe_few_tokens
     if _moe_few_tokens is None:
@@ -1099,9 +1237,11 @@ def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int 
         launches += 1       # the ordering is a launch of its own
 
 
-def moe_grouped(a, weight, out, offsets, order, *, top: int, first: bool) -> None:
+def moe_grouped(a, weight, out, offsets, order, *, top: int, first: bool, act: str = "silu", limit: float = 0.0,
+                alpha: float = 1.0) -> None:
     """The experts' products over the pairs in ``order``.  ``first``: a [T, K] (row = pair // top), weight [E, 2F, K]
-    (gate rows, then up rows) -> out[i] = silu(gate) * up for the i-th pair in order, [T*top, F].  Otherwise: a [T*top, K]
+    (gate rows, then up rows) -> out[i] = silu(gate) * up (``act`` "swiglu_clamp": the clamped form of gated_act, with
+    ``limit`` and ``alpha``) for the i-th pair in order, [T*top, F].  Otherwise: a [T*top, K]
     in that order, weight [E, N, K] -> out[pair] [T*top, N] 32-bit, by pair id."""
     _cuda("a", a, contiguous=False)
     _cuda("weight", weight, a.dtype)
@@ -1111,11 +1251,13 @@ def moe_grouped(a, weight, out, offsets, order, *, top: int, first: bool) -> Non
     N = rows // 2 if first else rows
     if a.shape[1] != K or tuple(out.shape) != (n_pairs, N) or offsets.numel() != E + 1:
         raise KernelError("moe_grouped: shapes do not fit")
+    if act not in ("silu", "swiglu_clamp") or (act == "swiglu_clamp" and not limit > 0):
+        raise KernelError(f"moe_grouped: activation {act!r} (limit {limit})")
     if (first and out.dtype != a.dtype) or (not first and out.dtype != torch.float32):
         raise KernelError("moe_grouped: the first product keeps the dtype, the second gives 32-bit")
     _call("mllm_moe_grouped", a.data_ptr(), _rows("a", a), weight.data_ptr(), out.data_ptr(), _rows("out", out),
           offsets.data_ptr(), order.data_ptr(), n_pairs, E, N, K, int(top) if first else 0, 0 if first else 1,
-          0 if first else 1, _dt(a), _stream())
+          0 if first else 1, _GATE_ACT[act], float(limit), float(alpha), _dt(a), _stream())
 
 
 def moe_combine(pair_out, weights, y, *, top: int, accumulate: bool) -> None:

@@ -179,3 +179,99 @@ class DistanceBiasAttention(ProjectedMixer):
 
 
 register_part("mixer", "distance_bias_attention", DistanceBiasAttention)
+
+
+class RotaryAttention(ProjectedMixer):
+    """Causal softmax attention with grouped key/value heads and key and value heads of different sizes, in which
+    queries and keys are normed and rotated before the scores are taken:
+
+    * ``qk_norm``: an RMS norm over the WHOLE query projection of a token (all heads at once) and another over the whole
+      key projection, each with a plain weight vector of that length and ``norm_eps`` inside the root;
+    * a rotation of the first ``rot_dims`` entries of every query and key head by position * base^(-2i / rot_dims);
+      ``rot_interleaved``: entry 2i pairs with 2i + 1, otherwise entry i with i + rot_dims / 2;
+    * score = (q . k) * scale over the keys j <= i that the mask leaves: all of them, the last ``window``, or (``chunk``)
+      those of the query's own block, block b being positions [b * chunk, (b + 1) * chunk) of the request;
+    * ``sink``: a trained scalar s_h per head; exp(s_h) is one more term of the softmax's denominator and of nothing else,
+      so part of a head's weight can go nowhere.
+
+    The keys are cached normed and rotated (rows padded to 16-byte pieces), so a cached token is never touched again.
+    With a chunk mask the pages of finished blocks go back to the pool as the request moves on.
+    """
+
+    in_names = ("q_weight", "k_weight", "v_weight")
+    out_name = "out_weight"
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float,
+                 norm_eps: float = 1e-6, qk_norm: bool = True, rot_dims: int = 0, rot_base: float = 10000.0,
+                 rot_interleaved: bool = True, window: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False):
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.qk_norm = bool(qk_norm)
+        self.rot_dims, self.rot_base, self.rot_interleaved = int(rot_dims), float(rot_base), bool(rot_interleaved)
+        self.window = None if window is None else int(window)
+        self.chunk = None if chunk is None else int(chunk)
+        self.has_sink = bool(sink)
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        if self.rot_dims < 0 or self.rot_dims % 2 or self.rot_dims > self.head_dim:
+            raise ValueError(f"rot_dims={rot_dims} must be even and at most head_dim={head_dim}")
+        if (self.window is not None and self.window < 1) or (self.chunk is not None and self.chunk < 1):
+            raise ValueError("window and chunk must be positive")
+        self.q_size = self.num_heads * self.head_dim
+        self.k_size = self.num_kv_heads * self.head_dim
+        self.v_size = self.num_kv_heads * self.v_head_dim
+        self.k_row = -(-self.head_dim // 8) * 8        # a key row in the pages: padded to 16-byte pieces, the padding zero
+        self.q_norm = self.k_norm = self.sink = self.freq = None
+
+    def param_specs(self):
+        p = {"q_weight": ParamSpec((self.q_size, self.hidden_size), "matrix"),
+             "k_weight": ParamSpec((self.k_size, self.hidden_size), "matrix"),
+             "v_weight": ParamSpec((self.v_size, self.hidden_size), "matrix"),
+             "out_weight": ParamSpec((self.hidden_size, self.num_heads * self.v_head_dim), "matrix")}
+        if self.qk_norm:
+            p["q_norm"] = ParamSpec((self.q_size,), "vector")
+            p["k_norm"] = ParamSpec((self.k_size,), "vector")
+        if self.has_sink:
+            p["sink"] = ParamSpec((self.num_heads,), "vector")
+        return p
+
+    def kernel_limits(self, dtype: str):
+        out = []
+        if not (1 <= self.head_dim <= 256):
+            out.append(f"rotary attention: key size {self.head_dim} is not between 1 and 256")
+        if not (1 <= self.v_head_dim <= 256):
+            out.append(f"rotary attention: value size {self.v_head_dim} is not between 1 and 256")
+        if (self.q_size + self.k_size) * 4 > 200 * 1024:
+            out.append(f"rotary attention: a token's {self.q_size} + {self.k_size} query and key entries do not fit the "
+                       f"shared memory of the kernel that norms and rotates them")
+        return out
+
+    def cache_need(self):
+        return PagedNeed(kv_heads=self.num_kv_heads, head_dim=self.k_row, window=self.window, chunk=self.chunk,
+                         v_head_dim=None if self.v_head_dim == self.k_row else self.v_head_dim)
+
+    def bind(self, params, rt) -> None:
+        import torch
+        from .rotary import rotary_table
+        super().bind(params, rt)
+        if not params:
+            return
+        if self.rot_dims:
+            f, _ = rotary_table(self.rot_dims, self.rot_base)       # float64 -> float32; the kernel takes position * f in 32-bit
+            self.freq = torch.tensor(f, dtype=torch.float64).float().contiguous().to(rt.device)
+
+    def core(self, proj, ctx, cache, out, out_scale: float = 1.0) -> None:
+        ops = self.rt.ops
+        gv = ctx.groups[cache.group]
+        q = ctx.ws.buf("attn_q", proj.shape[0], self.q_size, self.rt.act_dtype)
+        ops.qk_norm_rope(proj, 0, self.q_size, self.q_size + self.k_size, ctx, q, cache.k_pages, cache.v_pages,
+                         gv.slot_mapping if cache.write else None, heads=self.num_heads, kv_heads=self.num_kv_heads,
+                         head_dim=self.head_dim, v_head_dim=self.v_head_dim, q_norm=self.q_norm, k_norm=self.k_norm,
+                         eps=self.norm_eps, freq=self.freq, rot_dims=self.rot_dims, interleaved=self.rot_interleaved)
+        ops.biased_attention(q, cache.k_pages, cache.v_pages, gv.block_table, ctx, out, num_heads=self.num_heads,
+                             num_kv_heads=self.num_kv_heads, scale=self.scale, out_scale=out_scale, window=self.window,
+                             chunk=self.chunk, sink=self.sink)
+
+
+register_part("mixer", "rotary_attention", RotaryAttention)

@@ -1,6 +1,7 @@
 """Token embedding: x[t] = table[id_t] (+ the position table's row, fused into
 the same kernel when the position encoding is an additive table;
-src/kernels/embedding.cu:23-43).  The result is the 32-bit residual stream."""
+src/kernels/embedding.cu:23-43).  The result is the 32-bit residual stream; with ``copies`` > 1
+a token's row holds that many copies side by side: the start of a residual of several streams."""
 from __future__ import annotations
 
 import torch
@@ -9,17 +10,20 @@ from .base import Embedding, ParamSpec, register_part
 
 
 class TokenEmbedding(Embedding):
-    def __init__(self, hidden_size: int, vocab_size: int):
+    def __init__(self, hidden_size: int, vocab_size: int, copies: int = 1):
         self.hidden_size = int(hidden_size)
         self.vocab_size = int(vocab_size)
+        self.copies = int(copies)
+        if self.copies < 1:
+            raise ValueError("TokenEmbedding: copies must be at least 1")
 
     def param_specs(self):
         return {"table": ParamSpec((self.vocab_size, self.hidden_size), "table")}
 
     def forward(self, ctx, positions):
-        x = ctx.ws.buf("residual", ctx.T, self.hidden_size, torch.float32)
+        x = ctx.ws.buf("residual", ctx.T, self.hidden_size * self.copies, torch.float32)
         pos_table = positions.embedding_table() if positions is not None else None
-        self.rt.ops.embed(ctx.token_ids, ctx.positions, self.table, pos_table, x)
+        self.rt.ops.embed(ctx.token_ids, ctx.positions, self.table, pos_table, x, copies=self.copies)
         return x
 
 

@@ -3,7 +3,8 @@
 ``TiedHead`` multiplies by the token embedding's own [V, D] table, which is
 already laid out with the contraction dimension contiguous, so no transposed
 copy is made (the reference materialises wte_t [D, V] for its GEMM,
-src/model/gpt2_model.cu:87-113, 419-428).
+src/model/gpt2_model.cu:87-113, 419-428).  ``softcap`` c (or None): the logits are
+bent to c * tanh(logits / c) before they are handed out.
 """
 from __future__ import annotations
 
@@ -12,12 +13,22 @@ import torch
 from .base import Head, ParamSpec, register_part
 
 
+def _cap(softcap):
+    if softcap is None:
+        return None
+    c = float(softcap)
+    if not c > 0:
+        raise ValueError(f"head: the cap on the logits must be positive, got {softcap!r}")
+    return c
+
+
 class TiedHead(Head):
     accepts_lazy_norm = True
 
-    def __init__(self, hidden_size: int, vocab_size: int):
+    def __init__(self, hidden_size: int, vocab_size: int, softcap=None):
         self.hidden_size = int(hidden_size)
         self.vocab_size = int(vocab_size)
+        self.softcap = _cap(softcap)
         self.table = None
 
     def tie(self, embedding) -> None:
@@ -26,15 +37,18 @@ class TiedHead(Head):
     def forward(self, y, ctx):
         out = ctx.ws.logits(y.shape[0], self.vocab_size)
         self.rt.ops.linear(y, self.table, None, out=out)
+        if self.softcap is not None:
+            self.rt.ops.softcap(out, self.softcap)
         return out
 
 
 class LinearHead(Head):
     accepts_lazy_norm = True
 
-    def __init__(self, hidden_size: int, vocab_size: int):
+    def __init__(self, hidden_size: int, vocab_size: int, softcap=None):
         self.hidden_size = int(hidden_size)
         self.vocab_size = int(vocab_size)
+        self.softcap = _cap(softcap)
 
     def param_specs(self):
         return {"weight": ParamSpec((self.vocab_size, self.hidden_size), "matrix")}
@@ -42,6 +56,8 @@ class LinearHead(Head):
     def forward(self, y, ctx):
         out = ctx.ws.logits(y.shape[0], self.vocab_size)
         self.rt.ops.linear(y, self.weight, None, out=out)
+        if self.softcap is not None:
+            self.rt.ops.softcap(out, self.softcap)
         return out
 
 

@@ -1,0 +1,113 @@
+"""Hyper-connections: a residual of several parallel streams in place of the single residual sum.
+
+The residual of a token is ``streams`` vectors x_1 .. x_S side by side (a row of [S * D], 32-bit), all equal to the
+embedding at the start (``TokenEmbedding(copies=S)``).  Every sublayer (a mixer or a feed-forward) has a
+``HyperConnection`` with three learned tensors:
+
+    read    u = sum_s in[s] x_s                          the sublayer runs on norm(u)
+    write   x_t <- sum_s mix[s, t] x_s + out[t] * y      all streams at once from the old ones; y the sublayer's result
+
+The arrangement "hyper" wires a layer this way.  One kernel pass over a token's row does the write of one sublayer and
+the read and norm of the next, so a layer with a feed-forward is three such passes.  The model's last norm sees the
+plain sum of the streams (``StreamSumNorm``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import Join, Norm, ParamSpec, register_part
+from .block import _branch
+
+
+def _norm_args(norm):
+    """(gamma, beta or None, eps) of a LayerNorm or a plain-weight RMS norm part."""
+    beta = getattr(norm, "bias", None)
+    if beta is None and getattr(norm, "unit_offset", False):
+        return norm.gamma, None, norm.eps
+    return norm.weight, beta, norm.eps
+
+
+class HyperConnection(Join):
+    def __init__(self, hidden_size: int, streams: int):
+        self.hidden_size, self.streams = int(hidden_size), int(streams)
+        if self.streams < 1:
+            raise ValueError("HyperConnection: at least one stream")
+
+    def param_specs(self):
+        S = self.streams
+        return {"read": ParamSpec((S,), "vector"), "write": ParamSpec((S,), "vector"), "mix": ParamSpec((S, S), "vector")}
+
+    def kernel_limits(self, dtype: str):
+        from .. import ops
+        if self.streams > ops.HYPER_MAX_STREAMS:
+            return [f"hyper-connections: {self.streams} streams; the kernel takes up to {ops.HYPER_MAX_STREAMS}"]
+        return []
+
+    def read_norm(self, x, norm, ctx):
+        """h = norm(sum_s read[s] x_s) in the activation dtype."""
+        gamma, beta, eps = _norm_args(norm)
+        h = ctx.ws.buf("norm_out", x.shape[0], self.hidden_size, self.rt.act_dtype)
+        self.rt.ops.hyper_step(x, self.streams, in_weights=self.read, gamma=gamma, beta=beta, eps=eps, h=h)
+        return h
+
+    def forward(self, y, x, ctx, then=None):
+        """The write of this sublayer's result y into the streams x; with ``then`` = (the next sublayer's
+        HyperConnection, its norm) also that sublayer's read and norm of the new streams, which comes back."""
+        if then is None:
+            self.rt.ops.hyper_step(x, self.streams, y=y, mix=self.mix, out_weights=self.write)
+            return None
+        nxt, norm = then
+        gamma, beta, eps = _norm_args(norm)
+        h = ctx.ws.buf("norm_out", x.shape[0], self.hidden_size, self.rt.act_dtype)
+        self.rt.ops.hyper_step(x, self.streams, y=y, mix=self.mix, out_weights=self.write, in_weights=nxt.read, gamma=gamma,
+                               beta=beta, eps=eps, h=h)
+        return h
+
+
+register_part("join", "hyper_connection", HyperConnection)
+
+
+class StreamSumNorm(Norm):
+    """LayerNorm (weight and bias) of the sum of a residual's streams: what the head reads."""
+
+    def __init__(self, hidden_size: int, eps: float, streams: int):
+        self.hidden_size, self.eps, self.streams = int(hidden_size), float(eps), int(streams)
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.hidden_size,), "vector"), "bias": ParamSpec((self.hidden_size,), "vector")}
+
+    def forward(self, x, ctx, rows=None, lazy=False):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.ws.buf("norm_out", n, self.hidden_size, self.rt.act_dtype)
+        self.rt.ops.hyper_step(x, self.streams, gamma=self.weight, beta=self.bias, eps=self.eps, rows=rows, h=out)
+        return out
+
+    def stream_sum(self, x, ctx):
+        """The plain sum of the streams, [T, D] 32-bit (what a single-stream model calls its residual)."""
+        out = ctx.ws.buf("stream_sum", x.shape[0], self.hidden_size, torch.float32)
+        self.rt.ops.hyper_step(x, self.streams, sum_out=out)
+        return out
+
+
+register_part("norm", "stream_sum_layernorm", StreamSumNorm)
+
+
+def hyper(layer, x, ctx, cache):
+    """x: the streams [T, S * D].  Mixer, then feed-forward (if the layer has one), each read from and written to all
+    streams through its HyperConnection (``LayerSpec.mixer_join`` / ``ff_join``)."""
+    if layer.mixer_join is None or (layer.ff is not None and layer.ff_join is None):
+        raise RuntimeError("hyper arrangement: a sublayer has no HyperConnection")
+    D = layer.mixer_join.hidden_size
+    y = ctx.ws.buf("branch_out", x.shape[0], D, torch.float32)
+    h = layer.mixer_join.read_norm(x, layer.mixer_norm, ctx)
+    _branch(layer.mixer, y, h, ctx, cache)
+    if layer.ff is None:
+        layer.mixer_join.forward(y, x, ctx)
+        return x
+    h = layer.mixer_join.forward(y, x, ctx, then=(layer.ff_join, layer.ff_norm))
+    _branch(layer.ff, y, h, ctx)
+    layer.ff_join.forward(y, x, ctx)
+    return x
+
+
+register_part("arrangement", "hyper", lambda: hyper)

@@ -72,6 +72,7 @@ class GatedMLP(FeedForward):
             self.up_weight = self.gate_up_weight[self.inner_size:]
 
     accepts_lazy_norm = True
+    can_overwrite = True                # forward(..., accumulate=False) writes the result instead of adding it
 
     def project(self, h, ctx):
         """The first half: gate | up of h (a tensor or a norm not yet evaluated).  It only reads; an arrangement whose
@@ -80,14 +81,14 @@ class GatedMLP(FeedForward):
         self.rt.ops.linear(h, self.gate_up_weight, None, out=gu)
         return gu
 
-    def finish(self, gu, ctx, out_accum):
+    def finish(self, gu, ctx, out_accum, accumulate: bool = True):
         ops = self.rt.ops
         mid = ctx.ws.buf("ff_mid", gu.shape[0], self.inner_size, self.rt.act_dtype)
         ops.gated_act(gu, mid, self.activation)
-        ops.linear(mid, self.down_weight, None, out=out_accum, accumulate=True)
+        ops.linear(mid, self.down_weight, None, out=out_accum, accumulate=accumulate)
 
-    def forward(self, h, ctx, out_accum):
-        self.finish(self.project(h, ctx), ctx, out_accum)
+    def forward(self, h, ctx, out_accum, accumulate: bool = True):
+        self.finish(self.project(h, ctx), ctx, out_accum, accumulate)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -7,6 +7,12 @@ scores divided by their sum (+ 1e-20), and the output is the weighted sum of the
 W_down (act(W_gate h) * (W_up h)) without biases; a shared expert of the same form (``shared_size``, or None) runs
 for every token and is added.
 
+Variants, all constructor constants.  ``router_bias``: the logits get a trained offset per expert.
+``selection`` "softmax_top": no softmax over all experts; the ``top`` largest logits are chosen and weighted by the
+softmax over those alone (no groups).  ``activation`` "swiglu_clamp": an expert is W_down (g * sigmoid(alpha * g) *
+(u + 1)) with g = min(W_gate h, limit) and u = clamp(W_up h, -limit, limit); the shared expert has a limit of its own
+(``shared_limit``).
+
 Nothing is read back by the host: a kernel routes and orders the (token, choice) pairs by expert, and the experts'
 products run over that order with a grid that depends on the number of pairs only, so the step can be captured in a
 CUDA graph.  The experts' matrices are stacked at bind: [E, 2F, D] (gate rows, then up rows) and [E, D, F].
@@ -22,13 +28,26 @@ class MoEFeedForward(FeedForward):
     can_overwrite = True
 
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, groups: int = 1, keep: int = 1,
-                 shared_size: Optional[int] = None, activation: str = "silu"):
+                 shared_size: Optional[int] = None, activation: str = "silu", router_bias: bool = False,
+                 selection: str = "softmax_all", limit: float = 0.0, alpha: float = 1.0,
+                 shared_limit: Optional[float] = None):
         self.hidden_size, self.num_experts, self.top = int(hidden_size), int(num_experts), int(top)
         self.expert_size, self.groups, self.keep = int(expert_size), int(groups), int(keep)
         self.shared_size = None if shared_size is None else int(shared_size)
-        if activation != "silu":
-            raise ValueError("MoEFeedForward: the experts' activation is silu")
+        if activation not in ("silu", "swiglu_clamp"):
+            raise ValueError(f"MoEFeedForward: the experts' activation is silu or swiglu_clamp, got {activation!r}")
         self.activation = activation
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.shared_limit = self.limit if shared_limit is None else float(shared_limit)
+        if activation == "swiglu_clamp" and not (self.limit > 0 and self.shared_limit > 0):
+            raise ValueError("MoEFeedForward: the clamped activation needs positive limits")
+        self.has_router_bias = bool(router_bias)
+        if selection not in ("softmax_all", "softmax_top"):
+            raise ValueError(f"MoEFeedForward: selection is softmax_all or softmax_top, got {selection!r}")
+        if selection == "softmax_top" and self.groups != 1:
+            raise ValueError("MoEFeedForward: the softmax over the chosen logits takes no groups")
+        self.selection = selection
+        self.router_bias = None
         if self.num_experts % self.groups or not (1 <= self.keep <= self.groups):
             raise ValueError(f"MoEFeedForward: {self.num_experts} experts in {self.groups} groups, {self.keep} kept")
         if not (1 <= self.top <= self.keep * (self.num_experts // self.groups)):
@@ -37,6 +56,8 @@ class MoEFeedForward(FeedForward):
     def param_specs(self):
         D, F = self.hidden_size, self.expert_size
         p = {"router": ParamSpec((self.num_experts, D), "matrix")}
+        if self.has_router_bias:
+            p["router_bias"] = ParamSpec((self.num_experts,), "vector")
         for e in range(self.num_experts):
             p[f"expert{e}.gate"] = ParamSpec((F, D), "matrix")
             p[f"expert{e}.up"] = ParamSpec((F, D), "matrix")
@@ -61,6 +82,7 @@ class MoEFeedForward(FeedForward):
             return
         E = self.num_experts
         self.router = params["router"]
+        self.router_bias = params.get("router_bias")
         self.w_first = torch.stack([torch.cat([params[f"expert{e}.gate"], params[f"expert{e}.up"]], 0) for e in range(E)]).contiguous()
         self.w_second = torch.stack([params[f"expert{e}.down"] for e in range(E)]).contiguous()
         if self.shared_size is not None:
@@ -76,9 +98,11 @@ class MoEFeedForward(FeedForward):
         wts = ctx.ws.buf("moe_weights", T, top, torch.float32)
         order = ctx.ws.buf("moe_order", T, top, torch.int32)
         offsets = ctx.ws.buf("moe_offsets", 1, E + 1, torch.int32)
-        ops.moe_route(h, self.router, idx, wts, offsets, order, top=top, groups=self.groups, keep=self.keep)
+        ops.moe_route(h, self.router, idx, wts, offsets, order, top=top, groups=self.groups, keep=self.keep,
+                      bias=self.router_bias, mode=self.selection)
         mid = ctx.ws.buf("moe_mid", T * top, self.expert_size, self.rt.act_dtype)
-        ops.moe_grouped(h, self.w_first, mid, offsets, order, top=top, first=True)
+        ops.moe_grouped(h, self.w_first, mid, offsets, order, top=top, first=True, act=self.activation, limit=self.limit,
+                        alpha=self.alpha)
         pair_out = ctx.ws.buf("moe_pair_out", T * top, self.hidden_size, torch.float32)
         ops.moe_grouped(mid, self.w_second, pair_out, offsets, order, top=top, first=False)
         return pair_out, wts
@@ -89,7 +113,7 @@ class MoEFeedForward(FeedForward):
         gu = ctx.ws.buf("ff_gate_up", T, 2 * self.shared_size, self.rt.act_dtype)
         ops.linear(h, self.shared_first, None, out=gu)
         smid = ctx.ws.buf("ff_mid", T, self.shared_size, self.rt.act_dtype)
-        ops.gated_act(gu, smid, self.activation)
+        ops.gated_act(gu, smid, self.activation, limit=self.shared_limit, alpha=self.alpha)
         ops.linear(smid, self.shared_down, None, out=out, accumulate=accumulate)
 
     def forward_pairs(self, h, ctx, y):
