@@ -40,8 +40,8 @@ with "impl": "reference" and "dtype": "fp32".  The reference holds at most 16 re
 (more are cut) and there is no batch-64 point.  Where it cannot be built or run the line is
 {"impl": "reference", "unavailable": "<why>"}.
 
-``--compare-designs [small,medium,large]`` measures the engine's other designs, Finuvik and Falisun, beside GPT-2 at
-equal width, depth and head count (bfloat16 unless --dtype is given; ``--designs gpt2,falisun`` picks some of them).
+``--compare-designs [small,medium,large]`` measures the engine's other designs, Finuvik, Falisun and Mumopel, beside
+GPT-2 at equal width, depth and head count (bfloat16 unless --dtype is given; ``--designs gpt2,falisun`` picks some).
 
 ``--profile-step prefill|decode [--kernel-times]`` runs one small eager step (for a profiler, or to
 print each kernel's share of the step from CUDA events); ``--workload medium|xl`` runs the
@@ -316,7 +316,7 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: b
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
 
     cfg = dict(SMALL, n_layer=layers)
-    if design in ("finuvik", "falisun"):         # the same step of the other designs at the "small" comparison size
+    if design in ("finuvik", "falisun", "mumopel"):  # the same step of the other designs at the "small" comparison size
         cfg = design_configs("small")[design]
         cfg["layers"] = cfg["layers"][:layers]
         cfg["n_positions"], cfg["vocab_size"] = DESIGN_POSITIONS, cfg["vocab"]      # the names used below
@@ -469,7 +469,18 @@ def design_configs(size: str):
                 mixer["kv_from"] = first
             fl.append(dict(type="latent_attention", mixer=mixer, mlp=ffn))
     falisun = dict(architecture="Falisun", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), layers=fl)
-    return {"gpt2": gpt2, "finuvik": finuvik, "falisun": falisun}
+    # Mumopel at the same width, depth, heads and key/value heads as Finuvik's softmax branch: half of every head
+    # turns, the mask's blocks are 512 positions, a sink per head; two residual streams; the first layer's feed-forward
+    # is dense (Finuvik's inner size), the others route 2 of 8 clamped experts of a quarter of it beside a shared
+    # expert of half of it (Falisun's proportions); logits capped at 30
+    attn = dict(heads=H, kv_heads=z["kv_heads"], dim=dh, vdim=dh, scale=dh ** -0.5, rot=dict(base=10000.0, dims=dh // 2),
+                mask=dict(size=512))
+    routed = dict(kind="moe", router=dict(experts=8, top=2), expert=dict(ff=F // 4 // 8 * 8, limit=7.0),
+                  shared=dict(ff=F // 2 // 8 * 8, limit=7.0))
+    ml = [dict(type="attention", mixer=dict(attn), mlp=dict(kind="dense", ff=F) if i == 0 else routed) for i in range(L)]
+    mumopel = dict(architecture="Mumopel", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), layers=ml, streams=2,
+                   logit_softcap=30.0)
+    return {"gpt2": gpt2, "finuvik": finuvik, "falisun": falisun, "mumopel": mumopel}
 
 
 def _design_model(model_dir, dtype, batch, tokens):
@@ -574,7 +585,7 @@ def design_decode(model_dir, dtype, batch, steps):
 
 
 def run_compare_designs(sizes, dtype: str, batch: int, steps: int, designs=None) -> int:
-    """Prefill and decode throughput of Finuvik and Falisun beside GPT-2 at equal width, depth and head count, random
+    """Prefill and decode throughput of Finuvik, Falisun and Mumopel beside GPT-2 at equal width, depth and head count, random
     weights; one JSON line per size.  Per kernel entry point the line carries the
     microseconds of one eager step, from which the rooflines of the like kernels are compared."""
     import torch
@@ -732,8 +743,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64, prefill and other-precision measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
-    ap.add_argument("--design", choices=["gpt2", "finuvik", "falisun"], default="gpt2",
-                    help="with --profile-step: the model whose step is run (finuvik, falisun: the 'small' size of --compare-designs)")
+    ap.add_argument("--design", choices=["gpt2", "finuvik", "falisun", "mumopel"], default="gpt2",
+                    help="with --profile-step: the model whose step is run (the other designs: the 'small' size of --compare-designs)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --profile-step: time every launch of one eager step with CUDA events and print the shares")
     ap.add_argument("--attention", choices=["auto", "mma_sync"], default="auto",
@@ -741,9 +752,9 @@ def main() -> int:
     ap.add_argument("--workload", choices=["medium", "xl"],
                     help="run a continuous-batching workload of GPT-2 medium or XL instead of the benchmark")
     ap.add_argument("--compare-designs", nargs="?", const="small,medium,large", metavar="SIZES",
-                    help="measure Finuvik and Falisun beside GPT-2 at equal sizes (a comma list of small, medium, large) "
+                    help="measure Finuvik, Falisun and Mumopel beside GPT-2 at equal sizes (a comma list of small, medium, large) "
                          "instead of the benchmark: prefill of 2 x 1024 tokens and decode at --batch, one JSON line per size")
-    ap.add_argument("--designs", default="", help="with --compare-designs: a comma list of gpt2, finuvik, falisun (default: all)")
+    ap.add_argument("--designs", default="", help="with --compare-designs: a comma list of gpt2, finuvik, falisun, mumopel (default: all)")
     args = ap.parse_args()
     if args.compare_designs:
         sizes = [z for z in args.compare_designs.split(",") if z]

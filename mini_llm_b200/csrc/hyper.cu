@@ -4,9 +4,10 @@
 //   read    u = sum_s in[s] x_s                       then a norm of u feeds the sublayer
 //   write   x_t <- sum_s mix[s][t] x_s + out[t] * y   for all t at once, from the old streams; y the sublayer's result
 //
-// hyper_step does, per token and in one pass over its row: the write of the sublayer that has just run (if `y` is
-// given), then the read of the next sublayer from the new streams and its norm (if `h` is given): LayerNorm with weight
-// and bias, (u - mean) / sqrt(var + eps) * gamma + beta with the variance as the mean of the squared deviations, or an
+// hyper_step does, per token and in one pass over its row: the write of the sublayer that has just run (if `y` or
+// `pairs` is given; with `pairs` the result is y, if given, plus the weighted sum over the token's `top` chosen experts,
+// pairs[token * top + k] * pair_w[token * top + k] in the order of k: a routed feed-forward's last step), then the
+// read of the next sublayer from the new streams and its norm (if `h` is given): LayerNorm with weight and bias, (u - mean) / sqrt(var + eps) * gamma + beta with the variance as the mean of the squared deviations, or an
 // RMS norm (no centring, no bias) when beta is null.  With `in` null the read is the plain sum of the streams (what the
 // model's last norm sees).  `rows` gathers the tokens that are read (no write then).  Everything is 32-bit; h is
 // rounded to the activation dtype.  One CTA per token; u is kept in shared memory; the sums over s run in stream
@@ -21,7 +22,8 @@ template <typename TOut>
 __global__ void __launch_bounds__(256)
 hyper_step_kernel(float* x, const float* y, long long ldy, const float* __restrict__ mix, const float* __restrict__ outw,
                   const float* __restrict__ inw, const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
-                  const int* __restrict__ rows, TOut* h, long long ldh, float* sum_out, int S, int D) {
+                  const int* __restrict__ rows, TOut* h, long long ldh, float* sum_out, const float* pairs, const float* pair_w,
+                  int top, int S, int D) {
     extern __shared__ float u[];            // [D]
     __shared__ float scratch[33];
     __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS], s_in[MAX_STREAMS];
@@ -34,14 +36,18 @@ hyper_step_kernel(float* x, const float* y, long long ldy, const float* __restri
     const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     float* xr = x + r * (size_t)S * D;
     const float* yr = y ? y + (size_t)blockIdx.x * ldy : nullptr;
+    const float* pr = pairs ? pairs + (size_t)blockIdx.x * top * D : nullptr;
+    const float* pw = pairs ? pair_w + (size_t)blockIdx.x * top : nullptr;
+    const bool writes = yr != nullptr || pr != nullptr;
     const bool reads = h != nullptr || sum_out != nullptr;
     float part = 0.f;
     for (int d = tid; d < D; d += blockDim.x) {
         float xs[MAX_STREAMS];
 #pragma unroll
         for (int s = 0; s < MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * D + d] : 0.f;
-        if (yr) {
-            const float yv = yr[d];
+        if (writes) {
+            float yv = yr ? yr[d] : 0.f;
+            for (int k = 0; k < top; ++k) yv = fmaf(pw[k], pr[(size_t)k * D + d], yv);
             float nx[MAX_STREAMS];
 #pragma unroll
             for (int t = 0; t < MAX_STREAMS; ++t) {
@@ -85,27 +91,31 @@ MLLM_EXPORT int mllm_hyper_max_streams() { return MAX_STREAMS; }
 
 // x [., S * D] 32-bit.  y [R, D] 32-bit with mix [S * S] ([from][to]) and outw [S], or all null (no write).
 // h [R, D] (dtype) with gamma [D], beta [D] or null (RMS norm), inw [S] or null (plain sum), or null (no read);
-// sum_out [R, D] 32-bit or null: the read before its norm.  rows [R] or null.
+// sum_out [R, D] 32-bit or null: the read before its norm.  rows [R] or null.  pairs [R * top, D] with pair_w [R * top]
+// (32-bit), or null: the chosen experts' results and weights, summed into the written result.
 MLLM_EXPORT int mllm_hyper_step(float* x, const float* y, long long ldy, const float* mix, const float* outw, const float* inw,
                                 const float* gamma, const float* beta, float eps, const int* rows, void* h, long long ldh,
-                                float* sum_out, int R, int S, int D, int dtype, cudaStream_t stream) {
+                                float* sum_out, const float* pairs, const float* pair_w, int top, int R, int S, int D, int dtype,
+                                cudaStream_t stream) {
     if (R <= 0) return 0;
     if (S <= 0 || S > MAX_STREAMS || D <= 0) return mllm_fail(1, "hyper_step: %d streams of width %d (at most %d streams)", S, D, MAX_STREAMS);
-    if (y && (!mix || !outw)) return mllm_fail(1, "hyper_step: a write needs the mixing matrix and the output weights");
-    if (y && rows) return mllm_fail(1, "hyper_step: a write takes all rows");
+    if (!pairs) top = 0;
+    if (pairs && (!pair_w || top <= 0)) return mllm_fail(1, "hyper_step: the experts' results need their weights and a count");
+    if ((y || pairs) && (!mix || !outw)) return mllm_fail(1, "hyper_step: a write needs the mixing matrix and the output weights");
+    if ((y || pairs) && rows) return mllm_fail(1, "hyper_step: a write takes all rows");
     if (h && !gamma) return mllm_fail(1, "hyper_step: a norm needs its weight");
-    if (!y && !h && !sum_out) return 0;
+    if (!y && !pairs && !h && !sum_out) return 0;
     const size_t smem = sizeof(float) * (size_t)D;
     if (smem > 200 * 1024) return mllm_fail(1, "hyper_step: width %d does not fit shared memory", D);
     if (dtype == MLLM_F32) {
         if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(hyper_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         MLLM_CUDA(mllm_launch(hyper_step_kernel<float>, dim3(R), dim3(256), smem, stream, true, x, y, ldy, mix, outw, inw, gamma,
-                              beta, eps, rows, (float*)h, ldh, sum_out, S, D));
+                              beta, eps, rows, (float*)h, ldh, sum_out, pairs, pair_w, top, S, D));
     } else if (dtype == MLLM_BF16) {
         using bf = __nv_bfloat16;
         if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(hyper_step_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         MLLM_CUDA(mllm_launch(hyper_step_kernel<bf>, dim3(R), dim3(256), smem, stream, true, x, y, ldy, mix, outw, inw, gamma,
-                              beta, eps, rows, (bf*)h, ldh, sum_out, S, D));
+                              beta, eps, rows, (bf*)h, ldh, sum_out, pairs, pair_w, top, S, D));
     } else {
         return mllm_fail(1, "hyper_step: unknown dtype code %d", dtype);
     }

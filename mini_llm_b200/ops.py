@@ -102,7 +102,7 @@ def _signatures(lib):
                               c_void_p, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int,
                               c_int, c_int, c_void_p],
         "mllm_hyper_step": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
-                            c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                            c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_hyper_max_streams": [],
         "mllm_softcap": [c_void_p, c_ll, c_int, c_int, c_float, c_void_p],
         "mllm_gated_recurrence": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -931,12 +931,14 @@ HYPER_MAX_STREAMS = 8
 
 
 def hyper_step(x, streams: int, *, y=None, mix=None, out_weights=None, in_weights=None, gamma=None, beta=None, eps: float = 0.0,
-               rows=None, h=None, sum_out=None) -> None:
+               rows=None, h=None, sum_out=None, pairs=None) -> None:
     """One pass over a residual of ``streams`` streams, x [T, streams * D] (32-bit, changed in place).
 
     With ``y`` [T, D] (32-bit; the result of the sublayer that has just run), ``mix`` [streams, streams] ([from, to])
     and ``out_weights`` [streams]: x_t <- sum_s mix[s, t] x_s + out_weights[t] * y, all streams at once from the old
-    ones.  With ``h`` [R, D] (activation dtype) and ``gamma``: h = norm(sum_s in_weights[s] x_s) of the new streams
+    ones.  ``pairs`` = (results [T * top, D], weights [T, top], top), all 32-bit: the result written is y (if given) plus
+    the weighted sum over the token's ``top`` chosen experts in the order of the choices, which a routed feed-forward
+    leaves to this pass.  With ``h`` [R, D] (activation dtype) and ``gamma``: h = norm(sum_s in_weights[s] x_s) of the new streams
     (``in_weights`` None: the plain sum); LayerNorm with ``beta``, an RMS norm without.  ``sum_out`` [R, D] (32-bit)
     gets the read before its norm.  ``rows`` (int32 [R]) gathers the rows that are read (no write then)."""
     _cuda("x", x, torch.float32)
@@ -945,12 +947,24 @@ def hyper_step(x, streams: int, *, y=None, mix=None, out_weights=None, in_weight
         raise KernelError(f"hyper_step: {streams} streams (at most {HYPER_MAX_STREAMS}) in rows of {x.shape[1]}")
     D = x.shape[1] // streams
     R = T if rows is None else rows.numel()
+    writes = y is not None or pairs is not None
     if y is not None:
         _cuda("y", y, torch.float32, contiguous=False)
+        if tuple(y.shape) != (T, D):
+            raise KernelError("hyper_step: y does not fit the streams")
+    pair_out = pair_w = None
+    top = 0
+    if pairs is not None:
+        pair_out, pair_w, top = pairs
+        _cuda("pairs", pair_out, torch.float32)
+        _cuda("pair weights", pair_w, torch.float32)
+        if top < 1 or tuple(pair_out.shape) != (T * top, D) or pair_w.numel() != T * top:
+            raise KernelError("hyper_step: the experts' results or weights do not fit")
+    if writes:
         _cuda("mix", mix, torch.float32)
         _cuda("out_weights", out_weights, torch.float32)
-        if tuple(y.shape) != (T, D) or mix.numel() != streams * streams or out_weights.numel() != streams or rows is not None:
-            raise KernelError("hyper_step: y, mix or out_weights do not fit the streams")
+        if mix.numel() != streams * streams or out_weights.numel() != streams or rows is not None:
+            raise KernelError("hyper_step: mix or out_weights do not fit the streams")
     if rows is not None:
         _cuda("rows", rows, torch.int32)
     if in_weights is not None:
@@ -971,12 +985,13 @@ def hyper_step(x, streams: int, *, y=None, mix=None, out_weights=None, in_weight
         if tuple(sum_out.shape) != (R, D):
             raise KernelError("hyper_step: sum_out does not fit")
     _call("mllm_hyper_step", x.data_ptr(), y.data_ptr() if y is not None else None, _rows("y", y) if y is not None else 0,
-          mix.data_ptr() if y is not None else None, out_weights.data_ptr() if y is not None else None,
+          mix.data_ptr() if writes else None, out_weights.data_ptr() if writes else None,
           in_weights.data_ptr() if in_weights is not None else None, gamma.data_ptr() if h is not None else None,
           beta.data_ptr() if (h is not None and beta is not None) else None, float(eps),
           rows.data_ptr() if rows is not None else None, h.data_ptr() if h is not None else None,
-          _rows("h", h) if h is not None else 0, sum_out.data_ptr() if sum_out is not None else None, R, int(streams), D, dt,
-          _stream())
+          _rows("h", h) if h is not None else 0, sum_out.data_ptr() if sum_out is not None else None,
+          pair_out.data_ptr() if pairs is not None else None, pair_w.data_ptr() if pairs is not None else None, int(top), R,
+          int(streams), D, dt, _stream())
 
 
 def softcap(logits, cap: float) -> None:

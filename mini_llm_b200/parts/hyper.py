@@ -8,7 +8,8 @@ embedding at the start (``TokenEmbedding(copies=S)``).  Every sublayer (a mixer 
     write   x_t <- sum_s mix[s, t] x_s + out[t] * y      all streams at once from the old ones; y the sublayer's result
 
 The arrangement "hyper" wires a layer this way.  One kernel pass over a token's row does the write of one sublayer and
-the read and norm of the next, so a layer with a feed-forward is three such passes.  The model's last norm sees the
+the read and norm of the next, so a layer with a feed-forward is three such passes; the pass after a routed
+feed-forward also takes the weighted sum over the token's experts.  The model's last norm sees the
 plain sum of the streams (``StreamSumNorm``).
 """
 from __future__ import annotations
@@ -28,6 +29,8 @@ def _norm_args(norm):
 
 
 class HyperConnection(Join):
+    takes_pairs = True          # a routed feed-forward may leave the weighted sum over a token's experts to this pass
+
     def __init__(self, hidden_size: int, streams: int):
         self.hidden_size, self.streams = int(hidden_size), int(streams)
         if self.streams < 1:
@@ -50,17 +53,19 @@ class HyperConnection(Join):
         self.rt.ops.hyper_step(x, self.streams, in_weights=self.read, gamma=gamma, beta=beta, eps=eps, h=h)
         return h
 
-    def forward(self, y, x, ctx, then=None):
+    def forward(self, y, x, ctx, then=None, pairs=None):
         """The write of this sublayer's result y into the streams x; with ``then`` = (the next sublayer's
-        HyperConnection, its norm) also that sublayer's read and norm of the new streams, which comes back."""
+        HyperConnection, its norm) also that sublayer's read and norm of the new streams, which comes back.
+        ``pairs`` = (results per (token, choice), weights, top) of a routed feed-forward: their weighted sum is part of
+        the result (y may then be None)."""
         if then is None:
-            self.rt.ops.hyper_step(x, self.streams, y=y, mix=self.mix, out_weights=self.write)
+            self.rt.ops.hyper_step(x, self.streams, y=y, mix=self.mix, out_weights=self.write, pairs=pairs)
             return None
         nxt, norm = then
         gamma, beta, eps = _norm_args(norm)
         h = ctx.ws.buf("norm_out", x.shape[0], self.hidden_size, self.rt.act_dtype)
         self.rt.ops.hyper_step(x, self.streams, y=y, mix=self.mix, out_weights=self.write, in_weights=nxt.read, gamma=gamma,
-                               beta=beta, eps=eps, h=h)
+                               beta=beta, eps=eps, h=h, pairs=pairs)
         return h
 
 
@@ -105,8 +110,12 @@ def hyper(layer, x, ctx, cache):
         layer.mixer_join.forward(y, x, ctx)
         return x
     h = layer.mixer_join.forward(y, x, ctx, then=(layer.ff_join, layer.ff_norm))
-    _branch(layer.ff, y, h, ctx)
-    layer.ff_join.forward(y, x, ctx)
+    if hasattr(layer.ff, "forward_pairs"):
+        shared, pairs = layer.ff.forward_pairs(h, ctx, y)
+        layer.ff_join.forward(y if shared else None, x, ctx, pairs=pairs)
+    else:
+        _branch(layer.ff, y, h, ctx)
+        layer.ff_join.forward(y, x, ctx)
     return x
 
 
