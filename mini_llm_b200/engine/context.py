@@ -151,6 +151,9 @@ class StepContext:
         self.max_q_len = max(self.q_lens) if self.q_lens else 0
         self.max_ctx_len = max((a + b for a, b in zip(self.q_starts, self.q_lens)), default=0)
         self.decode_only = self.max_q_len == 1
+        # what a layer's arrangement leaves for the next one within the step (a residual write that the next layer's
+        # read takes along); nothing is carried from one step to the next
+        self.carry = None
 
 
 ATTN_TILE = 64      # query rows per tile of csrc/attention_flash.cu and attention_tiled.cu

@@ -940,7 +940,9 @@ def hyper_step(x, streams: int, *, y=None, mix=None, out_weights=None, in_weight
     the weighted sum over the token's ``top`` chosen experts in the order of the choices, which a routed feed-forward
     leaves to this pass.  With ``h`` [R, D] (activation dtype) and ``gamma``: h = norm(sum_s in_weights[s] x_s) of the new streams
     (``in_weights`` None: the plain sum); LayerNorm with ``beta``, an RMS norm without.  ``sum_out`` [R, D] (32-bit)
-    gets the read before its norm.  ``rows`` (int32 [R]) gathers the rows that are read (no write then)."""
+    gets the read before its norm.  ``rows`` (int32 [R]) gathers the tokens that are read; a write then takes place for
+    those tokens only, on the way to the read, and x is left as it was (a step's last write, when only the wanted tokens'
+    sum is read afterwards)."""
     _cuda("x", x, torch.float32)
     T = x.shape[0]
     if streams < 1 or streams > HYPER_MAX_STREAMS or x.shape[1] % streams:
@@ -963,7 +965,7 @@ def hyper_step(x, streams: int, *, y=None, mix=None, out_weights=None, in_weight
     if writes:
         _cuda("mix", mix, torch.float32)
         _cuda("out_weights", out_weights, torch.float32)
-        if mix.numel() != streams * streams or out_weights.numel() != streams or rows is not None:
+        if mix.numel() != streams * streams or out_weights.numel() != streams:
             raise KernelError("hyper_step: mix or out_weights do not fit the streams")
     if rows is not None:
         _cuda("rows", rows, torch.int32)

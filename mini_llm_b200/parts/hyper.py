@@ -8,9 +8,10 @@ embedding at the start (``TokenEmbedding(copies=S)``).  Every sublayer (a mixer 
     write   x_t <- sum_s mix[s, t] x_s + out[t] * y      all streams at once from the old ones; y the sublayer's result
 
 The arrangement "hyper" wires a layer this way.  One kernel pass over a token's row does the write of one sublayer and
-the read and norm of the next, so a layer with a feed-forward is three such passes; the pass after a routed
-feed-forward also takes the weighted sum over the token's experts.  The model's last norm sees the
-plain sum of the streams (``StreamSumNorm``).
+the read and norm of the next, also across layers: a layer leaves its last write to the next layer's first read
+(``ctx.carry``), so a layer is one pass per sublayer; the pass after a routed feed-forward also takes the weighted sum
+over the token's experts.  The model's last norm sees the plain sum of the streams (``StreamSumNorm``); it takes the last
+layer's write along for the tokens whose logits are wanted, and no others.
 """
 from __future__ import annotations
 
@@ -84,17 +85,52 @@ class StreamSumNorm(Norm):
     def forward(self, x, ctx, rows=None, lazy=False):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.buf("norm_out", n, self.hidden_size, self.rt.act_dtype)
-        self.rt.ops.hyper_step(x, self.streams, gamma=self.weight, beta=self.bias, eps=self.eps, rows=rows, h=out)
+        left = _take_carry(ctx, x)
+        if left is None:
+            self.rt.ops.hyper_step(x, self.streams, gamma=self.weight, beta=self.bias, eps=self.eps, rows=rows, h=out)
+        else:       # the last layer's write on the way, for the rows that are read (all of them when rows is None)
+            join, y, pairs = left
+            self.rt.ops.hyper_step(x, self.streams, y=y, mix=join.mix, out_weights=join.write, pairs=pairs, gamma=self.weight,
+                                   beta=self.bias, eps=self.eps, rows=rows, h=out)
         return out
 
     def stream_sum(self, x, ctx):
-        """The plain sum of the streams, [T, D] 32-bit (what a single-stream model calls its residual)."""
+        """The plain sum of the streams, [T, D] 32-bit (what a single-stream model calls its residual).  A write that
+        the last layer left open is made first, for all tokens."""
         out = ctx.ws.buf("stream_sum", x.shape[0], self.hidden_size, torch.float32)
-        self.rt.ops.hyper_step(x, self.streams, sum_out=out)
+        left = _take_carry(ctx, x)
+        if left is None:
+            self.rt.ops.hyper_step(x, self.streams, sum_out=out)
+        else:
+            join, y, pairs = left
+            self.rt.ops.hyper_step(x, self.streams, y=y, mix=join.mix, out_weights=join.write, pairs=pairs, sum_out=out)
         return out
 
 
 register_part("norm", "stream_sum_layernorm", StreamSumNorm)
+
+
+def _leave(ctx, x, join, y, pairs) -> None:
+    """A layer's last write stays open: whoever reads the streams next (the next layer, the model's last norm, or
+    ``StreamSumNorm.stream_sum``) makes it in the same pass.  y and the experts' results live in workspace buffers that
+    nothing touches before that read.  A context without a ``carry`` slot gets the write at once."""
+    if not hasattr(ctx, "carry"):
+        join.forward(y, x, ctx, pairs=pairs)
+        return
+    if ctx.carry is not None:
+        raise RuntimeError("hyper arrangement: a write is still open")
+    ctx.carry = (x, join, y, pairs)
+
+
+def _take_carry(ctx, x):
+    """(join, y, pairs) of the write that was left open on these streams, or None."""
+    left = getattr(ctx, "carry", None)
+    if left is None:
+        return None
+    if left[0] is not x and left[0].data_ptr() != x.data_ptr():
+        raise RuntimeError("hyper arrangement: the open write belongs to other streams")
+    ctx.carry = None
+    return left[1:]
 
 
 def hyper(layer, x, ctx, cache):
@@ -104,18 +140,23 @@ def hyper(layer, x, ctx, cache):
         raise RuntimeError("hyper arrangement: a sublayer has no HyperConnection")
     D = layer.mixer_join.hidden_size
     y = ctx.ws.buf("branch_out", x.shape[0], D, torch.float32)
-    h = layer.mixer_join.read_norm(x, layer.mixer_norm, ctx)
+    left = _take_carry(ctx, x)
+    if left is None:
+        h = layer.mixer_join.read_norm(x, layer.mixer_norm, ctx)
+    else:           # the layer before left its last write open: one pass makes it and this layer's first read
+        join, y_left, pairs = left
+        h = join.forward(y_left, x, ctx, then=(layer.mixer_join, layer.mixer_norm), pairs=pairs)
     _branch(layer.mixer, y, h, ctx, cache)
     if layer.ff is None:
-        layer.mixer_join.forward(y, x, ctx)
+        _leave(ctx, x, layer.mixer_join, y, None)
         return x
     h = layer.mixer_join.forward(y, x, ctx, then=(layer.ff_join, layer.ff_norm))
     if hasattr(layer.ff, "forward_pairs"):
         shared, pairs = layer.ff.forward_pairs(h, ctx, y)
-        layer.ff_join.forward(y if shared else None, x, ctx, pairs=pairs)
+        _leave(ctx, x, layer.ff_join, y if shared else None, pairs)
     else:
         _branch(layer.ff, y, h, ctx)
-        layer.ff_join.forward(y, x, ctx)
+        _leave(ctx, x, layer.ff_join, y, None)
     return x
 
 

@@ -377,7 +377,8 @@ def _hyper_want(x, S, y, mix, out_w, in_w, gamma, beta, eps):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,D,T", [(1, 64, 5), (2, 100, 37), (3, 320, 9), (4, 768, 130), (8, 24, 3), (2, 2048, 17)])
+@pytest.mark.parametrize("S,D,T", [(1, 64, 5), (2, 100, 37), (3, 320, 9), (4, 768, 130), (8, 24, 3), (2, 2048, 17), (5, 48, 4),
+                                   (7, 33, 2)])
 def test_stream_pass(ops, out_dtype, S, D, T):
     eps = 1e-5
     x0 = rnd(T, S * D, seed=S + D, scale=2.0) + 0.3
@@ -410,6 +411,40 @@ def test_stream_pass(ops, out_dtype, S, D, T):
     _, u, hw = _hyper_want(c(x), S, None, None, None, None, c(gamma), c(beta), eps)
     assert (c(s3) - u[rows.long().cpu()]).abs().max() < 2e-5 * max(1.0, u.abs().max().item())
     assert (c(h3) - hw[rows.long().cpu()]).abs().max() < tol * max(1.0, hw.abs().max().item())
+    # a write on the way to the read of gathered rows (one of them asked for twice): the same numbers as the write of
+    # all rows followed by the read, and the streams stay as they were
+    x4 = x0.clone()
+    h4, s4 = torch.empty(3, D, device=DEV, dtype=out_dtype), torch.empty(3, D, device=DEV)
+    ops.hyper_step(x4, S, y=y, mix=mix, out_weights=out_w, gamma=gamma, beta=beta, eps=eps, rows=rows, h=h4, sum_out=s4)
+    assert torch.equal(x4, x0) and torch.equal(s4, s3) and torch.equal(h4, h3)
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("with_y", [True, False])
+@pytest.mark.parametrize("S,D,T,top", [(2, 96, 11, 2), (3, 40, 5, 1), (6, 64, 3, 4)])
+def test_stream_pass_takes_the_experts_weighted_sum(ops, S, D, T, top, with_y):
+    """The written result is y (the shared expert's, if there is one) plus the sum over the token's chosen experts of
+    weight * result, for all rows and on the way to a read of gathered rows."""
+    eps = 1e-6
+    x0 = rnd(T, S * D, seed=S + top, scale=1.5)
+    y = rnd(T, D, seed=2) if with_y else None
+    pair_out, pair_w = rnd(T * top, D, seed=3, scale=2.0), torch.softmax(rnd(T, top, seed=4, scale=2.0), dim=1).contiguous()
+    mix = rnd(S, S, seed=5, scale=0.4) + 0.5 * torch.eye(S, device=DEV)
+    out_w, in_w = rnd(S, seed=6) + 0.3, rnd(S, seed=7, scale=0.5) + 0.5
+    gamma, beta = rnd(D, seed=8, scale=0.3) + 1.0, rnd(D, seed=9, scale=0.2)
+    c = lambda t: t.double().cpu()
+    total = (c(pair_out).view(T, top, D) * c(pair_w)[:, :, None]).sum(1) + (c(y) if with_y else 0.0)
+    new, _, hw = _hyper_want(c(x0), S, total, c(mix), c(out_w), c(in_w), c(gamma), c(beta), eps)
+    x, h = x0.clone(), torch.empty(T, D, device=DEV)
+    ops.hyper_step(x, S, y=y, mix=mix, out_weights=out_w, in_weights=in_w, gamma=gamma, beta=beta, eps=eps, h=h,
+                   pairs=(pair_out, pair_w, top))
+    assert (c(x).view(T, S, D) - new).abs().max() < 2e-5 * max(1.0, new.abs().max().item())
+    assert (c(h) - hw).abs().max() < 2e-5 * max(1.0, hw.abs().max().item())
+    rows = torch.tensor([T - 1, 1, 1], dtype=torch.int32, device=DEV)
+    x2, h2 = x0.clone(), torch.empty(3, D, device=DEV)
+    ops.hyper_step(x2, S, y=y, mix=mix, out_weights=out_w, in_weights=in_w, gamma=gamma, beta=beta, eps=eps, h=h2, rows=rows,
+                   pairs=(pair_out, pair_w, top))
+    assert torch.equal(x2, x0) and torch.equal(h2, h[rows.long()])
     ops.check_device_errors()
 
 
