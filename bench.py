@@ -470,11 +470,12 @@ def design_configs(size: str):
             fl.append(dict(type="latent_attention", mixer=mixer, mlp=ffn))
     falisun = dict(architecture="Falisun", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), layers=fl)
     # Mumopel at the same width, depth, heads and key/value heads as Finuvik's softmax branch: half of every head
-    # turns, the mask's blocks are 512 positions, a sink per head; two residual streams; the first layer's feed-forward
+    # turns, the mask's blocks are 768 positions (a 1,024-token prompt spans two blocks, and the decode steps after 512-token
+    # prompts see their whole context, as the other designs' do), a sink per head; two residual streams; the first layer's feed-forward
     # is dense (Finuvik's inner size), the others route 2 of 8 clamped experts of a quarter of it beside a shared
     # expert of half of it (Falisun's proportions); logits capped at 30
     attn = dict(heads=H, kv_heads=z["kv_heads"], dim=dh, vdim=dh, scale=dh ** -0.5, rot=dict(base=10000.0, dims=dh // 2),
-                mask=dict(size=512))
+                mask=dict(size=768))
     routed = dict(kind="moe", router=dict(experts=8, top=2), expert=dict(ff=F // 4 // 8 * 8, limit=7.0),
                   shared=dict(ff=F // 2 // 8 * 8, limit=7.0))
     ml = [dict(type="attention", mixer=dict(attn), mlp=dict(kind="dense", ff=F) if i == 0 else routed) for i in range(L)]
