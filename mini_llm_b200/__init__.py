@@ -1,4 +1,4 @@
-"""mini_llm_b200: a small, whole inference engine for one B200 (sm_100a): GPT-2, Finuvik, Falisun and Mumopel.
+"""mini_llm_b200: a small, whole inference engine for one B200 (sm_100a): GPT-2, Finuvik, Falisun, Mumopel and Kusirax.
 
 Configuration and registry (``config``), safetensors weights (``weights``), model
 parts and their assembly (``parts``, ``models``), paged cache manager (``cache``),
@@ -8,9 +8,9 @@ hand-written CUDA kernels (``csrc``, reached through ``ops``).
 from .config.base import (ConfigError, EngineConfig, config_from_dict, load_config, register_architecture,
                           registered_architectures)
 from .parts import (attention, block, embedding, head, hyper, join, latent, mlp, moe, norm, positions,  # noqa: F401
-                    projected, recurrent, ssm)                                                                     # (register the parts)
+                    projected, recurrent, ssm, wkv)                                                                # (register the parts)
 from .parts.base import register_part
-from .models import falisun, finuvik, gpt2, mumopel  # noqa: F401  (register GPT2LMHeadModel, Finuvik, Falisun, Mumopel)
+from .models import falisun, finuvik, gpt2, kusirax, mumopel  # noqa: F401  (register GPT2LMHeadModel, Finuvik, Falisun, Mumopel, Kusirax)
 from .weights.random_init import write_random_model
 from .sampling.params import SamplingParams
 from .engine.request import Request, RequestState, Response

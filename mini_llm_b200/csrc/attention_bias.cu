@@ -9,7 +9,11 @@
 // of the request and a query sees only keys of its own block); softmax over the visible keys, with exp(sink[h])
 // added to the denominator when a sink is given (a scalar per head: in the online softmax it is the starting maximum
 // with weight 1 and a value row of zeros); out_i = out_scale * sum_j p_ij v_j.
-// Either table, the window, the chunk and the sink may be absent.
+// Two more terms that a design may ask for: a cap on the scaled product before any bias is added, s <- c * tanh(s / c)
+// (`softcap` c > 0), and a linear distance penalty slope_h * (i - j) taken off the score (`slopes`, a number per head;
+// the product of the slope and the distance is taken in 32-bit in the kernel, so it needs no table and no bound on the
+// context).
+// Either table, the slopes, the cap, the window, the chunk and the sink may be absent.
 // Scores, biases, softmax and the weighted sum are 32-bit (expf, not the fast intrinsic) for both cache dtypes.
 //
 // Four kernels (the fourth, `mma`, is described where it stands).  `simt`: one warp per (token, head), 32 keys at a time: any step, and the plain twin of the
@@ -48,7 +52,12 @@ struct BiasArgs {
     int window;
     int chunk;                  // > 0: keys before floor(p / chunk) * chunk are not seen
     const float* sink;          // [H] or null: exp(sink[h]) joins the softmax denominator
+    float softcap;              // > 0: the scaled product s becomes softcap * tanh(s / softcap) before the biases
+    const float* slopes;        // [H] or null: slopes[h] * (i - j) is taken off the score
 };
+
+// the cap on a scaled product (before any bias)
+__device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
 
 // first key position that the query at position p sees
 __device__ __forceinline__ int first_visible(const BiasArgs& a, int p) {
@@ -67,6 +76,7 @@ __device__ __forceinline__ void warp_walk(const float* qs, const T* k_pages, con
     const int lane = threadIdx.x & 31;
     constexpr int NACC = MAX_D / 32;
     const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
+    const float slope = a.slopes ? a.slopes[h] : 0.f;
     for (int c0 = (k_lo / 32) * 32; c0 <= k_hi; c0 += 32) {
         const int kp = c0 + lane;
         const bool valid = kp >= k_lo && kp <= k_hi;
@@ -81,8 +91,9 @@ __device__ __forceinline__ void warp_walk(const float* qs, const T* k_pages, con
 #pragma unroll
                 for (int i = 0; i < 8; ++i) dot = fmaf(qs[d + i], kv[i], dot);
             }
-            s = dot * qf;
+            s = capped(dot * qf, a.softcap);
             if (brow) s += brow[p - kp];
+            if (a.slopes) s -= slope * (float)(p - kp);
         }
         const float m_new = fmaxf(m, warp_max(s));
         if (m_new == -INFINITY) continue;                 // no key of the chunk is in the range (uniform)
@@ -194,6 +205,7 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
     }
     const float qf = a.scale * (a.q_scale ? a.q_scale[p] : 1.0f);
     const float* brow = (a.dist_bias && live) ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
+    const float slope = (a.slopes && live) ? a.slopes[h] : 0.f;
     constexpr int NACC = MAX_D / 32;
     float acc[NACC];
 #pragma unroll
@@ -268,8 +280,9 @@ attention_bias_split_kernel(const T* q, long long q_stride, const T* k_pages, co
         }
         float sc = -INFINITY;
         if (valid) {
-            sc = dot * qf;
+            sc = capped(dot * qf, a.softcap);
             if (brow) sc += brow[p - kp];
+            if (a.slopes) sc -= slope * (float)(p - kp);
         }
         const float m_new = fmaxf(m, warp_max(sc));             // at least one key of the chunk is visible
         const float alpha = expf(m - m_new);
@@ -390,6 +403,8 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
     const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;          // rows 2ty, 2ty+1; keys 4tx..4tx+3; dims tx + 8i
     const int first_key = first_visible(a, pos0);           // of the tile's first row: later rows see no earlier key
     const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
+    const float slope = a.slopes ? a.slopes[h] : 0.f;
+    const bool biased = brow || a.slopes;
 
     for (int i = tid; i < BQ * dk; i += THREADS) {
         const int r = i / dk, d = i % dk;
@@ -444,10 +459,12 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
         }
         // distances between this query tile and this key tile: pos0 - (j*BK + BK-1) .. pos_max - j*BK
         const int dist0 = pos0 - (j * BK + BK - 1);
-        if (brow)
+        if (biased)
             for (int i = tid; i < BQ + BK; i += THREADS) {
                 const int dist = dist0 + i;
-                Bs[i] = (dist >= 0 && dist < a.n_dist) ? brow[dist] : 0.f;
+                float b = (brow && dist >= 0 && dist < a.n_dist) ? brow[dist] : 0.f;
+                if (a.slopes && dist >= 0) b -= slope * (float)dist;
+                Bs[i] = b;
             }
         __syncthreads();
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -470,8 +487,8 @@ attention_bias_tiled_kernel(const T* q, long long q_stride, const T* k_pages, co
             for (int c = 0; c < 4; ++c) {
                 const int kp = j * BK + 4 * tx + c;
                 const bool vis = kp <= qp && qp <= pos_max && kp >= first_visible(a, qp);
-                float sc = s[r][c];
-                if (brow && vis) sc += Bs[qp - kp - dist0];
+                float sc = capped(s[r][c], a.softcap);
+                if (biased && vis) sc += Bs[qp - kp - dist0];
                 s[r][c] = vis ? sc : -INFINITY;
                 mx = fmaxf(mx, s[r][c]);
             }
@@ -593,6 +610,8 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int first_key = first_visible(a, pos0);
     const float* brow = a.dist_bias ? a.dist_bias + (size_t)h * a.n_dist : nullptr;
+    const float slope = a.slopes ? a.slopes[h] : 0.f;
+    const bool biased = brow || a.slopes;
     const int kp8 = dk / 8, vp8 = dv / 8;
 
     // Which pieces of a tile this thread copies: the same (key, piece) pairs for every tile, so the divisions are
@@ -630,11 +649,13 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
                 cp_async16(vd + key * vrow + piece * 8, ok ? v_pages + row_of(kp) * dv + piece * 8 : v_pages, ok);
             }
         }
-        if (brow) {
+        if (biased) {
             const int dist0 = pos0 - (j * MK + MK - 1);
             for (int i = tid; i < MQ + MK; i += 128) {
                 const int dist = dist0 + i;
-                Bs[buf * (MQ + MK) + i] = (dist >= 0 && dist < a.n_dist) ? brow[dist] * LOG2E : 0.f;
+                float b = (brow && dist >= 0 && dist < a.n_dist) ? brow[dist] : 0.f;
+                if (a.slopes && dist >= 0) b -= slope * (float)dist;
+                Bs[buf * (MQ + MK) + i] = b * LOG2E;
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -649,8 +670,11 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
 
     const int r0 = warp * 16 + (lane >> 2);                      // this thread's rows: r0 and r0 + 8 of the tile
     const int qp0 = pos0 + r0, qp1 = qp0 + 8;
-    const float qf0 = a.scale * LOG2E * ((a.q_scale && r0 < rows) ? a.q_scale[qp0] : 1.0f);
-    const float qf1 = a.scale * LOG2E * ((a.q_scale && r0 + 8 < rows) ? a.q_scale[qp1] : 1.0f);
+    // with a cap the factors carry 1 / cap and the capped score is cap * log2 e * tanh(.)
+    const float unit = a.softcap > 0.f ? 1.0f / a.softcap : LOG2E;
+    const float capl = a.softcap * LOG2E;
+    const float qf0 = a.scale * unit * ((a.q_scale && r0 < rows) ? a.q_scale[qp0] : 1.0f);
+    const float qf1 = a.scale * unit * ((a.q_scale && r0 + 8 < rows) ? a.q_scale[qp1] : 1.0f);
     float o[NO][4];
 #pragma unroll
     for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -695,7 +719,8 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 float x0 = s[n][0] * qf0, x1 = s[n][1] * qf0, x2 = s[n][2] * qf1, x3 = s[n][3] * qf1;
-                if (brow) {
+                if (a.softcap > 0.f) { x0 = capl * tanhf(x0); x1 = capl * tanhf(x1); x2 = capl * tanhf(x2); x3 = capl * tanhf(x3); }
+                if (biased) {
                     x0 += b0[-n * 8]; x1 += b0[-n * 8 - 1]; x2 += b0[-n * 8 + 8]; x3 += b0[-n * 8 + 7];
                 }
                 s[n][0] = x0; s[n][1] = x1; s[n][2] = x2; s[n][3] = x3;
@@ -711,7 +736,8 @@ attention_bias_mma_kernel(const __nv_bfloat16* q, long long q_stride, const __nv
                     const int qp = (e < 2) ? qp0 : qp1;
                     const bool vis = kp <= qp && qp <= pos_max && kp >= first_visible(a, qp);
                     float sc = s[n][e] * ((e < 2) ? qf0 : qf1);
-                    if (brow && vis) sc += bs[qp - kp - dist0];
+                    if (a.softcap > 0.f) sc = capl * tanhf(sc);
+                    if (biased && vis) sc += bs[qp - kp - dist0];
                     sc = vis ? sc : -INFINITY;
                     s[n][e] = sc;
                     if (e < 2) mx0 = fmaxf(mx0, sc); else mx1 = fmaxf(mx1, sc);
@@ -802,13 +828,14 @@ MLLM_EXPORT int mllm_attention_bias(const void* q, long long q_stride, const voi
                                     const int* tiles, int n_tiles, void* out, long long out_stride, float* part_o,
                                     float* part_ml, int nsplit, int T, int H, int Hkv, int dkq, int dk, int dv, int page_size,
                                     float scale, float out_scale, const float* dist_bias, int n_dist,
-                                    const float* q_scale, int window, int chunk, const float* sink, int dtype, int impl,
-                                    cudaStream_t stream) {
+                                    const float* q_scale, int window, int chunk, const float* sink, float softcap,
+                                    const float* slopes, int dtype, int impl, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (int rc = check_sizes(H, Hkv, dk, dv, page_size, dtype)) return rc;
     if (dkq <= 0 || dkq > dk) return mllm_fail(1, "attention_bias: queries of %d against key rows of %d", dkq, dk);
     if (window < 0 || chunk < 0) return mllm_fail(1, "attention_bias: window %d, chunk %d", window, chunk);
-    BiasArgs a{dist_bias, n_dist, q_scale, scale, out_scale, window, chunk, sink};
+    if (!(softcap >= 0.f)) return mllm_fail(1, "attention_bias: a cap of %g on the scores", (double)softcap);
+    BiasArgs a{dist_bias, n_dist, q_scale, scale, out_scale, window, chunk, sink, softcap, slopes};
     const long long warps = (long long)T * H;
     const long long blocks = (warps + WARPS - 1) / WARPS;
     if (blocks > 2147483647LL) return mllm_fail(1, "attention_bias: too many (token, head) pairs");

@@ -12,7 +12,7 @@
 enum { MLLM_F32 = 0, MLLM_BF16 = 1 };
 // epilogue activation codes
 enum { MLLM_ACT_NONE = 0, MLLM_ACT_GELU_TANH = 1, MLLM_ACT_GELU_ERF = 2, MLLM_ACT_RELU = 3, MLLM_ACT_SILU = 4,
-       MLLM_ACT_SWIGLU_CLAMP = 5 };
+       MLLM_ACT_SWIGLU_CLAMP = 5, MLLM_ACT_RELU_SQ = 6 };
 
 // Records a message for mllm_last_error() and returns the code.
 int mllm_fail(int code, const char* fmt, ...);

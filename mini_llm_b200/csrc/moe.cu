@@ -5,11 +5,14 @@
 //                   those groups (the lowest index wins among equals), weights = scores / (their sum + 1e-20).
 //                   With `bias` a number per expert is added to the logits first.  `mode` 1: no softmax over all
 //                   experts: the `top` largest logits are chosen and the weights are the softmax over those alone.
+//                   `mode` 2: the scores are sigmoid(logit), each expert's on its own.  `group_sum` 2: a group's score is
+//                   the sum of its two largest scores instead of its largest.  The weights are multiplied by `w_scale`.
 //   moe_sort        one CTA: the (token, choice) pairs ordered by expert (a counting sort) and the experts' offsets;
 //                   with up to 16 tokens (decode steps) routing and ordering are one launch of one CTA.
 //   moe_grouped     out[row] = A[a_row] W_e^T for the pairs of expert e; a CTA finds its expert from the offsets on the
 //                   device, so the grid depends on the number of pairs only.  `gated`: W_e is [2F, K] (gate rows, then
-//                   up rows) and the result is act(gate) * up (silu, or the clamped form of gate_mul).  Three kernels: CUDA cores, 32 pairs x 64 columns per
+//                   up rows) and the result is act(gate) * up (silu, or the clamped form of gate_mul); an expert without a
+//                   gate has W_e [F, K] and an activation of one argument on the product (`uact`: the square of relu).  Three kernels: CUDA cores, 32 pairs x 64 columns per
 //                   CTA (32-bit weights, odd sizes); tensor cores, 64 x 64 (bfloat16); and for up to 32 pairs (decode
 //                   steps) a CTA per pair and 64 columns whose warps stream the weight rows.
 //   moe_combine     y[t] (+)= sum_k weight[t][k] * pair_out[t * top + k], in the order of k.
@@ -25,8 +28,8 @@ constexpr int MOE_FEW_PAIRS = 32;     // up to this many (token, choice) pairs e
 // One warp routes one token; `s` is the warp's E floats of shared memory.
 template <typename T>
 __device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr, const float* __restrict__ bias, int mode,
-                                            float* s, int D, int E, int top, int n_groups, int keep, int* idx, float* wout,
-                                            int lane) {
+                                            float* s, int D, int E, int top, int n_groups, int keep, int group_sum,
+                                            float w_scale, int* idx, float* wout, int lane) {
     constexpr int V = 16 / sizeof(T);                           // elements per 16-byte load
     const bool vec = D % V == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)Wr % 16 == 0;
     for (int e0 = 0; e0 < E; e0 += 4) {                         // four experts at a time: their loads are in flight together
@@ -87,23 +90,27 @@ __device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr
                 wsum += wout[k];
                 s[best] = -INFINITY;                             // taken
             }
-            for (int k = 0; k < top; ++k) wout[k] = wout[k] / wsum;
+            for (int k = 0; k < top; ++k) wout[k] = wout[k] / wsum * w_scale;
         }
         __syncwarp();
         return;
     }
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float v = expf(s[e] - mx);
-        s[e] = v;
-        sum += v;
+    if (mode == 2) {
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(s[e] - mx);
+            s[e] = v;
+            sum += v;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
     }
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
     __syncwarp();
     if (lane == 0) {
         // experts outside the kept groups are marked by a negative score (scores are >= 0)
@@ -115,8 +122,12 @@ __device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr
                 float bv = -1.f;
                 for (int g = 0; g < n_groups; ++g) {
                     if ((kept >> g) & 1ull) continue;
-                    float gm = -1.f;
-                    for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
+                    float gm = -1.f, g2 = 0.f;             // the largest score of the group and the one after it
+                    for (int e = g * per; e < (g + 1) * per; ++e) {
+                        if (s[e] > gm) { g2 = fmaxf(gm, 0.f); gm = s[e]; }
+                        else if (s[e] > g2) g2 = s[e];
+                    }
+                    if (group_sum == 2 && per > 1) gm += g2;
                     if (gm > bv) { bv = gm; best = g; }
                 }
                 if (best >= 0) kept |= 1ull << best;
@@ -136,7 +147,7 @@ __device__ __forceinline__ void route_token(const T* x, const T* __restrict__ Wr
             wsum += bv;
             s[best] = -8.f;                                  // taken
         }
-        for (int k = 0; k < top; ++k) wout[k] = wout[k] / (wsum + 1e-20f);
+        for (int k = 0; k < top; ++k) wout[k] = wout[k] / (wsum + 1e-20f) * w_scale;
     }
     __syncwarp();
 }
@@ -177,14 +188,14 @@ __device__ __forceinline__ void sort_pairs(const int* idx, int n, int E, int* of
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* h, long long ld, const T* __restrict__ Wr, const float* __restrict__ bias, int mode, int Tn, int D,
-                 int E, int top, int n_groups, int keep, int* idx, float* wout) {
+                 int E, int top, int n_groups, int keep, int group_sum, float w_scale, int* idx, float* wout) {
     extern __shared__ float sc[];
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= Tn) return;
-    route_token(h + (size_t)t * ld, Wr, bias, mode, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top,
-                wout + (size_t)t * top, lane);
+    route_token(h + (size_t)t * ld, Wr, bias, mode, sc + warp * E, D, E, top, n_groups, keep, group_sum, w_scale,
+                idx + (size_t)t * top, wout + (size_t)t * top, lane);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -199,22 +210,32 @@ moe_sort_kernel(const int* idx, int n, int E, int* offsets, int* sorted) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_sort_kernel(const T* h, long long ld, const T* __restrict__ Wr, const float* __restrict__ bias, int mode, int Tn,
-                      int D, int E, int top, int n_groups, int keep, int* idx, float* wout, int* offsets, int* sorted) {
+                      int D, int E, int top, int n_groups, int keep, int group_sum, float w_scale, int* idx, float* wout,
+                      int* offsets, int* sorted) {
     extern __shared__ float sc[];
     int* cnt = reinterpret_cast<int*>(sc + 8 * E);
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = warp; t < Tn; t += 8)
-        route_token(h + (size_t)t * ld, Wr, bias, mode, sc + warp * E, D, E, top, n_groups, keep, idx + (size_t)t * top,
-                    wout + (size_t)t * top, lane);
+        route_token(h + (size_t)t * ld, Wr, bias, mode, sc + warp * E, D, E, top, n_groups, keep, group_sum, w_scale,
+                    idx + (size_t)t * top, wout + (size_t)t * top, lane);
     __syncthreads();                                         // the CTA's own writes of idx are visible to all its threads
     sort_pairs(idx, Tn * top, E, offsets, sorted, cnt);
+}
+
+// an activation of one argument on a product (an expert without a gate); 0: none
+__device__ __forceinline__ float unary_act(float v, int uact) {
+    if (uact == MLLM_ACT_RELU_SQ) { const float r = fmaxf(v, 0.f); return r * r; }
+    if (uact == MLLM_ACT_RELU) return fmaxf(v, 0.f);
+    if (uact == MLLM_ACT_GELU_TANH) return gelu_tanh_f(v);
+    return v;
 }
 
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, long long ldo, const int* offsets,
-                   const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated, float limit, float alpha) {
+                   const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated, float limit, float alpha,
+                   int uact) {
     __shared__ float As[32][33];
     __shared__ float Ws[64][33];
     __shared__ float Us[64][33];
@@ -288,6 +309,7 @@ moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out
             if (n >= N) continue;
             float v = acc[j][i];
             if (gated) v = gate_mul(v, acu[j][i], gated, limit, alpha);
+            else v = unary_act(v, uact);
             out[(size_t)rows_o[r] * ldo + n] = from_f32<TO>(v);
         }
     }
@@ -300,7 +322,8 @@ moe_grouped_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, long long ldo, const int* offsets,
-                const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated, float limit, float alpha) {
+                const int* sorted, int E, int N, int K, int a_div, int out_by_pair, int gated, float limit, float alpha,
+                int uact) {
     extern __shared__ float xs[];                                // [K]
     __shared__ int s_e;
     pdl_wait();
@@ -359,6 +382,7 @@ moe_rows_kernel(const TA* A, long long lda, const TW* __restrict__ W, TO* out, l
     for (int u = 0; u < 8; ++u) {
         float v = warp_sum(acc[u]);
         if (gated) v = gate_mul(v, warp_sum(acu[u]), gated, limit, alpha);
+        else v = unary_act(v, uact);
         if (lane == 0 && n0 + u < N) out[orow + n0 + u] = from_f32<TO>(v);
     }
 }
@@ -477,6 +501,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* A, long long lda, const __nv_bfloat1
             if (r < cnt && col < N) {
                 float v = acc[n][c];
                 if (GATED) v = gate_mul(v, acu[n][c], act, limit, alpha);
+                else v = unary_act(v, act);
                 out[(size_t)rows_o[r] * ldo + col] = from_f32<TO>(v);
             }
         }
@@ -500,10 +525,11 @@ moe_combine_kernel(const float* pair_out, const float* w, float* y, long long ld
 MLLM_EXPORT int mllm_moe_max_experts() { return MAX_E; }
 
 MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, const float* bias, int mode, int Tn, int D, int E,
-                               int top, int n_groups, int keep, int* idx, float* w, int* offsets, int* sorted, int dtype,
-                               cudaStream_t stream) {
+                               int top, int n_groups, int keep, int group_sum, float w_scale, int* idx, float* w, int* offsets,
+                               int* sorted, int dtype, cudaStream_t stream) {
     if (Tn <= 0) return 0;
-    if (mode != 0 && mode != 1) return mllm_fail(1, "moe_route: unknown mode %d", mode);
+    if (mode < 0 || mode > 2) return mllm_fail(1, "moe_route: unknown mode %d", mode);
+    if (group_sum != 1 && group_sum != 2) return mllm_fail(1, "moe_route: a group's score is its largest score or the sum of its two largest, not of %d", group_sum);
     if (mode == 1 && n_groups != 1) return mllm_fail(1, "moe_route: the softmax over the chosen logits takes no groups");
     if (E < 1 || E > MAX_E || top < 1 || top > E) return mllm_fail(1, "moe_route: %d experts (at most %d), top %d", E, MAX_E, top);
     if (n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || n_groups > 64)
@@ -513,11 +539,11 @@ MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, cons
         const size_t smem = (size_t)8 * E * 4 + (size_t)(E + 1) * 4;
         if (dtype == MLLM_F32)
             MLLM_CUDA(mllm_launch(moe_route_sort_kernel<float>, dim3(1), dim3(256), smem, stream, true, (const float*)h, ld,
-                                  (const float*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, idx, w, offsets, sorted));
+                                  (const float*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, group_sum, w_scale, idx, w, offsets, sorted));
         else if (dtype == MLLM_BF16)
             MLLM_CUDA(mllm_launch(moe_route_sort_kernel<__nv_bfloat16>, dim3(1), dim3(256), smem, stream, true,
                                   (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, bias, mode, Tn, D, E, top, n_groups, keep,
-                                  idx, w, offsets, sorted));
+                                  group_sum, w_scale, idx, w, offsets, sorted));
         else
             return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
         return 0;
@@ -525,10 +551,11 @@ MLLM_EXPORT int mllm_moe_route(const void* h, long long ld, const void* Wr, cons
     const size_t smem = (size_t)4 * E * 4;
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(moe_route_kernel<float>, dim3((Tn + 3) / 4), dim3(128), smem, stream, true, (const float*)h, ld,
-                              (const float*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, idx, w));
+                              (const float*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, group_sum, w_scale, idx, w));
     else if (dtype == MLLM_BF16)
         MLLM_CUDA(mllm_launch(moe_route_kernel<__nv_bfloat16>, dim3((Tn + 3) / 4), dim3(128), smem, stream, true,
-                              (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, bias, mode, Tn, D, E, top, n_groups, keep, idx, w));
+                              (const __nv_bfloat16*)h, ld, (const __nv_bfloat16*)Wr, bias, mode, Tn, D, E, top, n_groups, keep,
+                              group_sum, w_scale, idx, w));
     else
         return mllm_fail(1, "moe_route: unknown dtype code %d", dtype);
     MLLM_CUDA(mllm_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, true, (const int*)idx, Tn * top, E, offsets, sorted));
@@ -539,7 +566,9 @@ MLLM_EXPORT int mllm_moe_few_tokens() { return MOE_FEW_TOKENS; }
 
 // kind 0: A in `dtype`, gated, out in `dtype` (the experts' first product with its activation `act`: MLLM_ACT_SILU, or
 // MLLM_ACT_SWIGLU_CLAMP with `limit` and `alpha`);
-// kind 1: A in `dtype`, out 32-bit (the experts' second product).
+// kind 1: A in `dtype`, out 32-bit (the experts' second product);
+// kind 2: A in `dtype`, no gate, out in `dtype` = act(A W_e^T) with an activation of one argument (MLLM_ACT_RELU_SQ ...):
+// the first product of experts without a gate.
 MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, const int* offsets,
                                  const int* sorted, int n_pairs, int E, int N, int K, int a_div, int out_by_pair, int kind,
                                  int act, float limit, float alpha, int dtype, cudaStream_t stream) {
@@ -547,7 +576,11 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
     const dim3 grid((n_pairs + 31) / 32 + E, (N + 63) / 64), block(256);
     if (grid.y > 65535) return mllm_fail(1, "moe_grouped: too many columns");
     if (kind == 0 && act != MLLM_ACT_SILU && act != MLLM_ACT_SWIGLU_CLAMP) return mllm_fail(1, "moe_grouped: activation code %d", act);
+    if (kind == 2 && act != MLLM_ACT_RELU_SQ && act != MLLM_ACT_RELU && act != MLLM_ACT_GELU_TANH)
+        return mllm_fail(1, "moe_grouped: activation code %d of an expert without a gate", act);
+    if (kind < 0 || kind > 2) return mllm_fail(1, "moe_grouped: kind %d", kind);
     const int gated = kind == 0 ? act : 0;
+    const int uact = kind == 2 ? act : 0;
     if (n_pairs <= MOE_FEW_PAIRS && (size_t)K * 4 <= 96 * 1024) {
         const dim3 fg(n_pairs, (N + 63) / 64);
         const size_t smem = (size_t)K * 4;
@@ -559,10 +592,10 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
                 raised = true;                                                                                           \
             }                                                                                                            \
             MLLM_CUDA(mllm_launch(moe_rows_kernel<TA, TW, TO>, fg, block, smem, stream, true, (const TA*)A, lda, (const TW*)W, \
-                                  (TO*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated, limit, alpha));    \
+                                  (TO*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated, limit, alpha, uact)); \
         } while (0)
         if (dtype == MLLM_F32) MLLM_ROWS(float, float, float);
-        else if (dtype == MLLM_BF16 && kind == 0) MLLM_ROWS(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+        else if (dtype == MLLM_BF16 && kind != 1) MLLM_ROWS(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
         else if (dtype == MLLM_BF16) MLLM_ROWS(__nv_bfloat16, __nv_bfloat16, float);
         else return mllm_fail(1, "moe_grouped: unknown dtype code %d", dtype);
 #undef MLLM_ROWS
@@ -580,6 +613,10 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
             MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<__nv_bfloat16, 1>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A,
                                   lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, act, limit,
                                   alpha));
+        } else if (kind == 2) {
+            constexpr size_t smem = (size_t)2 * (GM + GN) * GROW * 2;
+            MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<__nv_bfloat16, 0>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A, lda,
+                                  (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, act, 0.f, 0.f));
         } else {
             constexpr size_t smem = (size_t)2 * (GM + GN) * GROW * 2;
             MLLM_CUDA(mllm_launch(moe_grouped_mma_kernel<float, 0>, mg, dim3(128), smem, stream, true, (const __nv_bfloat16*)A, lda,
@@ -589,15 +626,15 @@ MLLM_EXPORT int mllm_moe_grouped(const void* A, long long lda, const void* W, vo
     }
     if (dtype == MLLM_F32)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<float, float, float>, grid, block, 0, stream, true, (const float*)A, lda,
-                              (const float*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated, limit, alpha));
-    else if (dtype == MLLM_BF16 && kind == 0)
+                              (const float*)W, (float*)out, ldo, offsets, sorted, E, N, K, a_div, out_by_pair, gated, limit, alpha, uact));
+    else if (dtype == MLLM_BF16 && kind != 1)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, true,
                               (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, offsets, sorted, E,
-                              N, K, a_div, out_by_pair, gated, limit, alpha));
+                              N, K, a_div, out_by_pair, gated, limit, alpha, uact));
     else if (dtype == MLLM_BF16)
         MLLM_CUDA(mllm_launch(moe_grouped_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, block, 0, stream, true,
                               (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (float*)out, ldo, offsets, sorted, E, N, K,
-                              a_div, out_by_pair, gated, limit, alpha));
+                              a_div, out_by_pair, gated, limit, alpha, uact));
     else
         return mllm_fail(1, "moe_grouped: unknown dtype code %d", dtype);
     return 0;

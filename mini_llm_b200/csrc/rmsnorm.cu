@@ -157,7 +157,63 @@ join_kernel(const float* y, long long y_stride, const float* pairs, const float*
     for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = from_f32<TOut>(rowbuf[d] / r2 * (nw[d] + noff));
 }
 
+// The join of a block that norms after the sum: with v = y[r] (+ sum_k pw[r][k] * pairs[r * top + k], the weighted results
+// of a routed feed-forward's chosen experts, in the order of k; y or the pairs may be absent, and both: v = 0),
+//   x[r] <- (alpha * x[r] + v) / sqrt(mean((alpha * x[r] + v)^2) + eps) * w,
+// all 32-bit, in place; h (if given) gets the new x in the activation dtype, for the products that read it next.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+post_norm_kernel(const float* y, long long y_stride, const float* pairs, const float* pw, int top, const float* __restrict__ w,
+                 float alpha, float* x, long long x_stride, TOut* h, long long h_stride, int D, float eps) {
+    extern __shared__ float rowbuf[];       // [D]
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch();
+    const size_t r = blockIdx.x;
+    float* xr = x + r * x_stride;
+    float q = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = y ? y[r * y_stride + d] : 0.f;
+        if (pairs)
+            for (int k = 0; k < top; ++k) v = fmaf(pw[r * top + k], pairs[(r * top + k) * D + d], v);
+        v = fmaf(alpha, xr[d], v);
+        rowbuf[d] = v;
+        q = fmaf(v, v, q);
+    }
+    const float rr = sqrtf(block_sum(q, scratch) / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = rowbuf[d] / rr * w[d];
+        xr[d] = v;
+        if (h) h[r * h_stride + d] = from_f32<TOut>(v);
+    }
+}
+
 }  // namespace
+
+MLLM_EXPORT int mllm_post_norm(const float* y, long long y_stride, const float* pairs, const float* pw, int top, const float* w,
+                               float alpha, float* x, long long x_stride, void* h, long long h_stride, int R, int D, float eps,
+                               int h_dtype, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (D <= 0 || (size_t)D * 4 > 200 * 1024) return mllm_fail(1, "post_norm: width %d", D);
+    if (pairs && (!pw || top <= 0)) return mllm_fail(1, "post_norm: pairs without their weights");
+    const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : ((D + 31) / 32) * 32);
+    const size_t smem = (size_t)D * 4;
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        MLLM_CUDA(cudaFuncSetAttribute(post_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        MLLM_CUDA(cudaFuncSetAttribute(post_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    if (h && h_dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(post_norm_kernel<__nv_bfloat16>, dim3(R), dim3(threads), smem, stream, true, y, y_stride, pairs, pw,
+                              top, w, alpha, x, x_stride, (__nv_bfloat16*)h, h_stride, D, eps));
+    else if (!h || h_dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(post_norm_kernel<float>, dim3(R), dim3(threads), smem, stream, true, y, y_stride, pairs, pw, top, w,
+                              alpha, x, x_stride, (float*)h, h_stride, D, eps));
+    else
+        return mllm_fail(1, "post_norm: unknown dtype code %d", h_dtype);
+    return 0;
+}
 
 MLLM_EXPORT int mllm_norm_scale_add(const float* y, long long y_stride, const float* pairs, const float* pw, int top,
                                     const float* w, const float* ls, float* x, long long x_stride, const float* nw,

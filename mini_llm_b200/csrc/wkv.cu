@@ -1,0 +1,252 @@
+// A linear recurrence with a matrix state per head, a decay per key channel that depends on the token, and a bonus for
+// the current token (RWKV-style time mixing).  Per head, with r_t, k_t, v_t rows of n entries and S [n, n] zero at the
+// start of a sequence:
+//   w_t = exp(-exp(W2 tanh(l_t) + w0))                 l_t: a low-rank projection of the token (R entries), W2 [n, R]
+//   o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t          the bonus u counts for the current token only
+//   S_t = diag(w_t) S_(t-1) + k_t v_t^T
+//   y_t = o_t / sqrt(mean(o_t^2) + eps) * g * silu(z_t)   g: a weight per channel, z: the gate's projection
+// The inputs of the five projections are mixes of a token's row with the row before it: m_s = h + (h' - h) * mu_s, h'
+// the previous token's h (zeros before the first token); the last row of a step is kept in the request's state next
+// to S, so that the next step finds it.  State, decay (tanh, both exponentials), the update, o, the norm and the gate
+// are 32-bit whatever the dtype of the projections.
+//
+// Three kernels.  `shift`: the mixes of every token (one CTA per token).  `scan`: a CTA takes 32 columns of one
+// (request, head)'s state; thread (lane, g) keeps rows g*WR .. g*WR+WR-1 of column lane in registers for the whole walk,
+// tokens come CH at a time (r, k, the decays and v staged in shared memory), the row groups' partial outputs meet in
+// group order; every element of the state is a recurrence of its own, so the state after n tokens is the same bits
+// however the tokens were cut into steps.  `finish`: one warp per (token, head): the unit norm, the weight and the gate.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WKV_CH = 16;          // tokens per chunk of the scan
+constexpr int WKV_COLS = 32;        // columns of the state a CTA takes
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+wkv_shift_kernel(const T* h, long long ldh, const float* __restrict__ mu, const float* state, long long state_stride,
+                 long long prev_off, const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                 const int* __restrict__ slots, const int* __restrict__ positions, T* __restrict__ mixes, int Tn, int D, int NS) {
+    pdl_wait();
+    pdl_launch();
+    const int t = blockIdx.x;
+    const int seq = token_seq[t];
+    const bool inside = t > cu_q[seq];                          // the row before is a token of this step
+    const bool has_state = positions[t] > 0;                    // else: the first token of a sequence sees zeros
+    const T* cur = h + (size_t)t * ldh;
+    const T* before = h + (size_t)(t - (inside ? 1 : 0)) * ldh;
+    const float* kept = state + (size_t)slots[seq] * state_stride + prev_off;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float x = to_f32(cur[d]);
+        const float p = inside ? to_f32(before[d]) : (has_state ? kept[d] : 0.f);
+        const float diff = p - x;
+        for (int s = 0; s < NS; ++s)
+            mixes[((size_t)s * Tn + t) * D + d] = from_f32<T>(fmaf(diff, mu[(size_t)s * D + d], x));
+    }
+}
+
+struct WkvArgs {
+    const int* cu_q;        // [S+1] first flat token of every request of the step
+    const int* slots;       // [S] state slot of every request
+    const float* w0;        // [Hr*n]
+    const float* u;         // [Hr*n]
+    float* state;           // [slots][state_stride]: S of every head [Hr][n][n], then the last row of h at prev_off
+    long long state_stride, prev_off;
+    long long r_stride, k_stride, v_stride, l_stride, o_stride, h_stride;
+    int Hr, n, R, D, write_state;
+};
+
+// grid (requests, heads, ceil(n / 32)); block (32, G), G = ceil(n / WR).  o [T][Hr*n] float.
+template <typename T, int WR>
+__global__ void __launch_bounds__(1024)
+wkv_scan_kernel(const T* r, const T* k, const T* v, const T* low, const T* __restrict__ W2, const T* h, float* __restrict__ o,
+                WkvArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int n = a.n, R = a.R, G = blockDim.y, np = G * WR;    // rows padded to a multiple of WR: the padding has r = k = 0, w = 1
+    float* rs = sm;                           // [CH][np]
+    float* ks = rs + WKV_CH * np;             // [CH][np]
+    float* ws = ks + WKV_CH * np;             // [CH][np]
+    float* vs = ws + WKV_CH * np;             // [CH][32]
+    float* tl = vs + WKV_CH * WKV_COLS;       // [CH][R]   tanh of the low-rank projection
+    float* os = tl + WKV_CH * R;              // [G][CH][32]
+    pdl_wait();
+    pdl_launch();
+    const int seq = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * WKV_COLS;
+    const int lane = threadIdx.x, g = threadIdx.y, tid = g * 32 + lane, nthreads = G * 32;
+    const int t0 = a.cu_q[seq], t1 = a.cu_q[seq + 1];
+    if (t1 <= t0) return;
+    const int slot = a.slots[seq];
+    const int j = j0 + lane;
+    const bool col = j < n;
+    float* sp = a.state + (size_t)slot * a.state_stride + ((size_t)hd * n) * n + j;
+    float s[WR], uu[WR];
+#pragma unroll
+    for (int i = 0; i < WR; ++i) {
+        const int row = g * WR + i;
+        s[i] = (col && row < n) ? sp[(size_t)row * n] : 0.f;
+        uu[i] = row < n ? a.u[hd * n + row] : 0.f;
+    }
+    // the row that the next step's first token mixes with: the last row of h of this step
+    if (a.write_state && hd == 0 && blockIdx.z == 0) {
+        float* kept = a.state + (size_t)slot * a.state_stride + a.prev_off;
+        const T* last = h + (size_t)(t1 - 1) * a.h_stride;
+        for (int d = tid; d < a.D; d += nthreads) kept[d] = to_f32(last[d]);
+    }
+    for (int c0 = t0; c0 < t1; c0 += WKV_CH) {
+        const int nc = min(WKV_CH, t1 - c0);
+        __syncthreads();                      // the chunk before is no longer read
+        for (int idx = tid; idx < nc * R; idx += nthreads) {
+            const int c = idx / R, q = idx % R;
+            tl[c * R + q] = tanhf(to_f32(low[(size_t)(c0 + c) * a.l_stride + q]));
+        }
+        for (int idx = tid; idx < nc * np; idx += nthreads) {
+            const int c = idx / np, i = idx % np;
+            float rv = 0.f, kv = 0.f;
+            if (i < n) {
+                rv = to_f32(r[(size_t)(c0 + c) * a.r_stride + (size_t)hd * n + i]);
+                kv = to_f32(k[(size_t)(c0 + c) * a.k_stride + (size_t)hd * n + i]);
+            }
+            rs[c * np + i] = rv;
+            ks[c * np + i] = kv;
+        }
+        for (int idx = tid; idx < nc * WKV_COLS; idx += nthreads) {
+            const int c = idx / WKV_COLS, d = idx % WKV_COLS;
+            vs[idx] = j0 + d < n ? to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)hd * n + j0 + d]) : 0.f;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nc * np; idx += nthreads) {
+            const int c = idx / np, i = idx % np;
+            float w = 1.f;
+            if (i < n) {
+                float dot = a.w0[hd * n + i];
+                const T* wr = W2 + ((size_t)hd * n + i) * R;
+                const float* tc = tl + c * R;
+                for (int q = 0; q < R; ++q) dot = fmaf(to_f32(wr[q]), tc[q], dot);
+                w = expf(-expf(dot));
+            }
+            ws[c * np + i] = w;
+        }
+        __syncthreads();
+        for (int c = 0; c < nc; ++c) {
+            const float vj = vs[c * WKV_COLS + lane];
+            const float* rr = rs + c * np + g * WR;
+            const float* kk = ks + c * np + g * WR;
+            const float* ww = ws + c * np + g * WR;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < WR; ++i) {
+                const float kv = kk[i] * vj;
+                acc = fmaf(rr[i], fmaf(uu[i], kv, s[i]), acc);
+                s[i] = fmaf(ww[i], s[i], kv);
+            }
+            os[(g * WKV_CH + c) * WKV_COLS + lane] = acc;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nc * WKV_COLS; idx += nthreads) {       // the row groups meet in group order
+            const int c = idx / WKV_COLS, d = idx % WKV_COLS;
+            if (j0 + d >= n) continue;
+            float acc = os[c * WKV_COLS + d];
+            for (int gg = 1; gg < G; ++gg) acc += os[(gg * WKV_CH + c) * WKV_COLS + d];
+            o[(size_t)(c0 + c) * a.o_stride + (size_t)hd * n + j0 + d] = acc;
+        }
+    }
+    if (a.write_state && col) {
+#pragma unroll
+        for (int i = 0; i < WR; ++i)
+            if (g * WR + i < n) sp[(size_t)(g * WR + i) * n] = s[i];
+    }
+}
+
+// one warp per (token, head): y = o / sqrt(mean(o^2) + eps) * weight * silu(z)
+template <typename T>
+__global__ void __launch_bounds__(128)
+wkv_finish_kernel(const float* o, long long o_stride, const T* z, long long z_stride, const float* __restrict__ weight,
+                  T* __restrict__ y, long long y_stride, int Tn, int Hr, int n, float eps) {
+    pdl_wait();
+    pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long gw = (long long)blockIdx.x * 4 + warp;
+    if (gw >= (long long)Tn * Hr) return;
+    const int t = (int)(gw / Hr), hd = (int)(gw % Hr);
+    const float* orow = o + (size_t)t * o_stride + (size_t)hd * n;
+    float ss = 0.f;
+    for (int d = lane; d < n; d += 32) { const float x = orow[d]; ss = fmaf(x, x, ss); }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+    for (int d = lane; d < n; d += 32) {
+        const float zz = to_f32(z[(size_t)t * z_stride + (size_t)hd * n + d]);
+        y[(size_t)t * y_stride + (size_t)hd * n + d] = from_f32<T>(orow[d] * inv * weight[hd * n + d] * (zz / (1.0f + expf(-zz))));
+    }
+}
+
+}  // namespace
+
+MLLM_EXPORT int mllm_wkv_max_dim() { return 256; }
+
+// mixes [NS][T][D] = h + (row before - h) * mu[s]; the row before a step's first token of a request is the one kept in
+// its state (zeros at position 0).
+MLLM_EXPORT int mllm_wkv_shift(const void* h, long long ldh, const float* mu, const float* state, long long state_stride,
+                               long long prev_off, const int* token_seq, const int* cu_q, const int* slots,
+                               const int* positions, void* mixes, int T, int D, int NS, int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D <= 0 || NS <= 0) return mllm_fail(1, "wkv_shift: width %d, %d mixes", D, NS);
+    if (dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(wkv_shift_kernel<float>, dim3(T), dim3(256), 0, stream, true, (const float*)h, ldh, mu, state,
+                              state_stride, prev_off, token_seq, cu_q, slots, positions, (float*)mixes, T, D, NS));
+    else if (dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(wkv_shift_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, true, (const __nv_bfloat16*)h, ldh,
+                              mu, state, state_stride, prev_off, token_seq, cu_q, slots, positions, (__nv_bfloat16*)mixes, T, D, NS));
+    else
+        return mllm_fail(1, "wkv_shift: unknown dtype code %d", dtype);
+    return 0;
+}
+
+// r, k, v [T, Hr*n], low [T, R], W2 [Hr*n, R] in `dtype`; w0, u [Hr*n] float; h [T, D] (its last row of every request is
+// kept); state [slots][state_stride] float with S at 0 and the kept row at prev_off; o [T, Hr*n] float.
+MLLM_EXPORT int mllm_wkv_scan(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
+                              long long v_stride, const void* low, long long l_stride, const void* W2, const float* w0,
+                              const float* u, const void* h, long long h_stride, float* state, long long state_stride,
+                              long long prev_off, const int* cu_q, const int* slots, float* o, long long o_stride, int S,
+                              int Hr, int n, int R, int D, int write_state, int dtype, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    if (Hr <= 0 || n <= 0 || n > 256 || R <= 0) return mllm_fail(1, "wkv_scan: %d heads of %d, rank %d", Hr, n, R);
+    if (Hr > 65535) return mllm_fail(1, "wkv_scan: grid of %d x %d", S, Hr);
+    const int WR = n <= 64 ? 2 : (n <= 128 ? 4 : 8);
+    const int G = (n + WR - 1) / WR, np = G * WR;
+    const size_t smem = sizeof(float) * ((size_t)3 * WKV_CH * np + WKV_CH * WKV_COLS + (size_t)WKV_CH * R + (size_t)G * WKV_CH * WKV_COLS);
+    if (smem > 200 * 1024) return mllm_fail(1, "wkv_scan: heads of %d with rank %d need %zu bytes of shared memory", n, R, smem);
+    WkvArgs a{cu_q, slots, w0, u, state, state_stride, prev_off, r_stride, k_stride, v_stride, l_stride, o_stride, h_stride,
+              Hr, n, R, D, write_state};
+    const dim3 grid(S, Hr, (n + WKV_COLS - 1) / WKV_COLS), block(32, G);
+#define MLLM_WKV(TT, WRR)                                                                                                \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024)                                                                                            \
+            MLLM_CUDA(cudaFuncSetAttribute(wkv_scan_kernel<TT, WRR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MLLM_CUDA(mllm_launch(wkv_scan_kernel<TT, WRR>, grid, block, smem, stream, true, (const TT*)r, (const TT*)k,    \
+                              (const TT*)v, (const TT*)low, (const TT*)W2, (const TT*)h, o, a));                         \
+    } while (0)
+    if (dtype == MLLM_F32) {
+        if (WR == 2) MLLM_WKV(float, 2); else if (WR == 4) MLLM_WKV(float, 4); else MLLM_WKV(float, 8);
+    } else if (dtype == MLLM_BF16) {
+        if (WR == 2) MLLM_WKV(__nv_bfloat16, 2); else if (WR == 4) MLLM_WKV(__nv_bfloat16, 4); else MLLM_WKV(__nv_bfloat16, 8);
+    } else {
+        return mllm_fail(1, "wkv_scan: unknown dtype code %d", dtype);
+    }
+#undef MLLM_WKV
+    return 0;
+}
+
+MLLM_EXPORT int mllm_wkv_finish(const float* o, long long o_stride, const void* z, long long z_stride, const float* weight,
+                                void* y, long long y_stride, int T, int Hr, int n, float eps, int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const long long blocks = ((long long)T * Hr + 3) / 4;
+    if (blocks > 2147483647LL) return mllm_fail(1, "wkv_finish: too many (token, head) pairs");
+    if (dtype == MLLM_F32)
+        MLLM_CUDA(mllm_launch(wkv_finish_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, stream, true, o, o_stride,
+                              (const float*)z, z_stride, weight, (float*)y, y_stride, T, Hr, n, eps));
+    else if (dtype == MLLM_BF16)
+        MLLM_CUDA(mllm_launch(wkv_finish_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, stream, true, o, o_stride,
+                              (const __nv_bfloat16*)z, z_stride, weight, (__nv_bfloat16*)y, y_stride, T, Hr, n, eps));
+    else
+        return mllm_fail(1, "wkv_finish: unknown dtype code %d", dtype);
+    return 0;
+}

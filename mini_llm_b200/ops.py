@@ -25,6 +25,7 @@ _FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}      # what the products' epilogues take
 _GATE_ACT = {"gelu_tanh": 1, "gelu_erf": 2, "relu": 3, "silu": 4, "swiglu_clamp": 5}   # what gated_act takes
+_UNGATED_ACT = {"relu_sq": 6}     # activations of one argument that the experts' first product takes (experts without a gate)
 _lib = None
 
 c_int, c_ll, c_float, c_void_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
@@ -97,10 +98,21 @@ def _signatures(lib):
         "mllm_attention_bias_split_keys": [],
         "mllm_attention_bias": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+                                c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_int,
+                                c_int, c_void_p],
         "mllm_qk_norm_rope": [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                               c_void_p, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                              c_int, c_int, c_void_p],
+                              c_int, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
+        "mllm_post_norm": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_ll, c_void_p, c_ll, c_int,
+                           c_int, c_float, c_int, c_void_p],
+        "mllm_wkv_shift": [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_wkv_scan": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_ll, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_void_p],
+        "mllm_wkv_finish": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int,
+                            c_void_p],
+        "mllm_wkv_max_dim": [],
         "mllm_hyper_step": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                             c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_hyper_max_streams": [],
@@ -125,8 +137,8 @@ def _signatures(lib):
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_gated_group_norm": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int,
                                   c_void_p],
-        "mllm_moe_route": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                           c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+        "mllm_moe_route": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_moe_grouped": [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
         "mllm_moe_combine": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
@@ -794,14 +806,15 @@ _bias_split_keys = None
 
 
 def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, num_kv_heads, scale, dist_bias=None,
-                     q_scale=None, out_scale: float = 1.0, window=None, chunk=None, sink=None,
-                     impl: Optional[str] = None) -> None:
+                     q_scale=None, out_scale: float = 1.0, window=None, chunk=None, sink=None, softcap: float = 0.0,
+                     slopes=None, impl: Optional[str] = None) -> None:
     """Causal attention over the cache with keys and values of different sizes, an additive score bias
     ``dist_bias[head, i - j]`` (float32 [heads, n]) and a factor ``q_scale[position]`` (float32 [n]) on the query:
     out[t] = out_scale * softmax_j((q_t . k_j) * scale * q_scale[p_t] + dist_bias[h, p_t - j]) v_j.
     ``window``: only the last ``window`` keys are seen; ``chunk``: only keys from floor(p_t / chunk) * chunk on (block b is
     positions [b * chunk, (b + 1) * chunk) of the request); ``sink`` (float32 [heads]): exp(sink[h]) is one more
-    term of the softmax's denominator and of nothing else.
+    term of the softmax's denominator and of nothing else.  ``softcap`` c > 0: the scaled product s becomes
+    c * tanh(s / c) before any bias is added; ``slopes`` (float32 [heads]): slopes[h] * (p_t - j) is taken off the score.
 
     q [T, heads * dkq], k_pages [P, kv_heads, page_size, dk] with dk >= dkq a multiple of 8 (key rows padded with
     zeros), v_pages [P, kv_heads, page_size, dv], out [T, heads * dv] (rows contiguous; a column slice of a wider
@@ -840,6 +853,10 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
         _cuda("sink", sink, torch.float32)
         if sink.numel() != num_heads:
             raise KernelError("biased_attention: one sink per query head")
+    if slopes is not None:
+        _cuda("slopes", slopes, torch.float32)
+        if slopes.numel() != num_heads:
+            raise KernelError("biased_attention: one slope per query head")
     if impl is None:
         impl = "simt"
         if getattr(ctx, "decode_only", False):
@@ -872,7 +889,8 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
           out.data_ptr(), ldo, part_o, part_ml, nsplit, T, num_heads, num_kv_heads, dkq, dk, dv, ps, float(scale),
           float(out_scale), dist_bias.data_ptr() if dist_bias is not None else None, n_dist,
           q_scale.data_ptr() if q_scale is not None else None, int(window or 0), int(chunk or 0),
-          sink.data_ptr() if sink is not None else None, _dt(q), {"simt": 0, "tiled": 1, "split": 2, "mma": 3}[impl],
+          sink.data_ptr() if sink is not None else None, float(softcap or 0.0),
+          slopes.data_ptr() if slopes is not None else None, _dt(q), {"simt": 0, "tiled": 1, "split": 2, "mma": 3}[impl],
           _stream())
     if impl == "split":
         global launches
@@ -883,7 +901,8 @@ def biased_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, n
 # --------------------------------------------------------------------------- normed and rotated queries and keys
 def qk_norm_rope(proj, q_off: int, k_off: int, v_off: int, ctx, q_out, k_pages, v_pages, slot_mapping, *, heads: int,
                  kv_heads: int, head_dim: int, v_head_dim: int, q_norm=None, k_norm=None, eps: float = 0.0, freq=None,
-                 rot_dims: int = 0, interleaved: bool = True) -> None:
+                 rot_dims: int = 0, interleaved: bool = True, head_norm: bool = False, v_first=None, v_lambda=None,
+                 v_keep=None) -> None:
     """What stands between a Q | K | V projection and attention when queries and keys are normed and rotated.
 
     proj [T, .] holds a token's queries at column q_off (heads * head_dim), keys at k_off (kv_heads * head_dim) and
@@ -892,7 +911,10 @@ def qk_norm_rope(proj, q_off: int, k_off: int, v_off: int, ctx, q_out, k_pages, 
     ``rot_dims`` entries of every head turn by position * freq[i] (float32 [rot_dims / 2]); ``interleaved``: entry 2i
     pairs with 2i + 1, else i with i + rot_dims / 2.  Queries go to q_out [T, heads * head_dim]; keys (rows of the
     pages may be padded) and values go to the tokens' slots (``slot_mapping`` None: nothing is cached).  All 32-bit
-    up to the final rounding."""
+    up to the final rounding.  ``head_norm`` (instead of q_norm / k_norm): after the rotation every query head and every
+    key head is divided by its own root mean square (eps inside the root, no weights).  ``v_first`` [T, kv_heads *
+    v_head_dim] with ``v_lambda`` (a float32 scalar on the device): the values become (1 - lambda) v + lambda v_first
+    before they are cached; ``v_keep`` [T, kv_heads * v_head_dim] gets the values as they are cached."""
     _cuda("proj", proj, contiguous=False)
     _cuda("q_out", q_out, proj.dtype, contiguous=False)
     T = proj.shape[0]
@@ -909,6 +931,17 @@ def qk_norm_rope(proj, q_off: int, k_off: int, v_off: int, ctx, q_out, k_pages, 
         _cuda("freq", freq, torch.float32)
         if rot_dims % 2 or rot_dims > head_dim or freq.numel() != rot_dims // 2:
             raise KernelError(f"qk_norm_rope: {rot_dims} rotated entries of {head_dim}, {freq.numel()} frequencies")
+    if head_norm and (q_norm is not None or k_norm is not None):
+        raise KernelError("qk_norm_rope: the per-head norm takes no weights")
+    for name, t in (("v_first", v_first), ("v_keep", v_keep)):
+        if t is not None:
+            _cuda(name, t, proj.dtype, contiguous=False)
+            if tuple(t.shape) != (T, nv):
+                raise KernelError(f"qk_norm_rope: {name} {tuple(t.shape)} against {nv} value columns")
+    if v_first is not None:
+        _cuda("v_lambda", v_lambda, torch.float32)
+        if v_lambda.numel() != 1:
+            raise KernelError("qk_norm_rope: v_lambda is one number")
     dkp, ps = head_dim, 1
     if slot_mapping is not None:
         _cuda("k_pages", k_pages, proj.dtype)
@@ -923,7 +956,10 @@ def qk_norm_rope(proj, q_off: int, k_off: int, v_off: int, ctx, q_out, k_pages, 
           k_norm.data_ptr() if k_norm is not None else None, float(eps), freq.data_ptr() if rot_dims else None,
           int(rot_dims), int(bool(interleaved)), ctx.positions.data_ptr(), q_out.data_ptr(), _rows("q_out", q_out),
           k_pages.data_ptr() if slot_mapping is not None else None, v_pages.data_ptr() if slot_mapping is not None else None,
-          int(dkp), slot_mapping.data_ptr() if slot_mapping is not None else None, int(ps), T, _dt(proj), _stream())
+          int(dkp), slot_mapping.data_ptr() if slot_mapping is not None else None, int(ps), int(bool(head_norm)),
+          v_first.data_ptr() if v_first is not None else None, _rows("v_first", v_first) if v_first is not None else 0,
+          v_lambda.data_ptr() if v_first is not None else None, v_keep.data_ptr() if v_keep is not None else None,
+          _rows("v_keep", v_keep) if v_keep is not None else 0, T, _dt(proj), _stream())
 
 
 # --------------------------------------------------------------------------- a residual of several streams
@@ -1038,6 +1074,98 @@ def norm_scale_add(y, weight, scale, x, eps: float, *, pairs=None, pair_weights=
           next_weight.data_ptr() if next_weight is not None else None, float(next_offset), float(next_eps),
           next_out.data_ptr() if next_weight is not None else None, _rows("next_out", next_out) if next_weight is not None else 0,
           R, D, float(eps), _dt(next_out) if next_weight is not None else F32, _stream())
+
+
+def post_norm(x, weight, eps: float, alpha: float, *, y=None, pairs=None, pair_weights=None, top: int = 0, h=None) -> None:
+    """x <- (alpha * x + v) / sqrt(mean((alpha * x + v)^2) + eps) * weight, row by row, all 32-bit, in place: the join of a
+    block that norms after the sum.  v = y (32-bit [T, D], or None), plus sum_k pair_weights[t, k] * pairs[t * top + k]
+    when ``pairs`` [T * top, D] is given (the chosen experts' results of a routed feed-forward).  ``h`` [T, D]
+    (float32 or bfloat16, or None) gets the new x for the products that read it next."""
+    _cuda("x", x, torch.float32, contiguous=False)
+    _cuda("weight", weight, torch.float32)
+    R, D = x.shape
+    if weight.numel() != D:
+        raise KernelError(f"post_norm: x {tuple(x.shape)}, weight {weight.numel()}")
+    if y is not None:
+        _cuda("y", y, torch.float32, contiguous=False)
+        if tuple(y.shape) != (R, D):
+            raise KernelError(f"post_norm: y {tuple(y.shape)}, x {tuple(x.shape)}")
+    if pairs is not None:
+        _cuda("pairs", pairs, torch.float32)
+        _cuda("pair_weights", pair_weights, torch.float32)
+        if tuple(pairs.shape) != (R * top, D) or pair_weights.numel() != R * top:
+            raise KernelError("post_norm: pairs do not fit")
+    if h is not None:
+        _cuda("h", h, contiguous=False)
+        if tuple(h.shape) != (R, D):
+            raise KernelError("post_norm: h does not fit x")
+    _call("mllm_post_norm", y.data_ptr() if y is not None else None, _rows("y", y) if y is not None else 0,
+          pairs.data_ptr() if pairs is not None else None, pair_weights.data_ptr() if pairs is not None else None, int(top),
+          weight.data_ptr(), float(alpha), x.data_ptr(), _rows("x", x), h.data_ptr() if h is not None else None,
+          _rows("h", h) if h is not None else 0, R, D, float(eps), _dt(h) if h is not None else F32, _stream())
+
+
+# --------------------------------------------------------------------------- a recurrence with token-dependent decay
+WKV_MAX_DIM = 256       # largest head size of csrc/wkv.cu
+
+
+def wkv_shift(h, mu, state, prev_off: int, ctx, mixes) -> None:
+    """mixes[s, t] = h[t] + (h'[t] - h[t]) * mu[s] for the step's tokens, h' the row before: the token before it in the step,
+    or (for a request's first token of the step) the row kept in its state at column ``prev_off`` (zeros at position 0).
+    h [T, D], mu float32 [NS, D], state float32 [slots, row], mixes [NS, T, D] in h's dtype."""
+    _cuda("h", h, contiguous=False)
+    _cuda("mu", mu, torch.float32)
+    _cuda("state", state, torch.float32)
+    _cuda("mixes", mixes, h.dtype)
+    T, D = h.shape
+    NS = mu.shape[0]
+    if tuple(mu.shape) != (NS, D) or tuple(mixes.shape) != (NS, T, D) or state.dim() != 2 or prev_off + D > state.shape[1]:
+        raise KernelError(f"wkv_shift: h {tuple(h.shape)}, mu {tuple(mu.shape)}, mixes {tuple(mixes.shape)}, state {tuple(state.shape)}")
+    _call("mllm_wkv_shift", h.data_ptr(), _rows("h", h), mu.data_ptr(), state.data_ptr(), state.stride(0), int(prev_off),
+          ctx.token_seq.data_ptr(), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), ctx.positions.data_ptr(),
+          mixes.data_ptr(), T, D, NS, _dt(h), _stream())
+
+
+def wkv_scan(r, k, v, low, w2, w0, u, h, state, prev_off: int, ctx, out, *, heads: int, write_state: bool = True) -> None:
+    """The recurrence of csrc/wkv.cu over the step's tokens, request by request: w = exp(-exp(w2 tanh(low) + w0));
+    o = (S + diag(u) k v^T)^T r; S <- diag(w) S + k v^T.  r, k, v [T, heads * n], low [T, R], w2 [heads * n, R] in one
+    dtype; w0, u float32 [heads * n]; state float32 [slots, row] with S [heads, n, n] at column 0 and the last row of h
+    [T, D] of every request kept at column ``prev_off``; out float32 [T, heads * n]."""
+    _cuda("r", r, contiguous=False)
+    for name, t in (("k", k), ("v", v), ("low", low), ("h", h)):
+        _cuda(name, t, r.dtype, contiguous=False)
+    _cuda("w2", w2, r.dtype)
+    _cuda("w0", w0, torch.float32)
+    _cuda("u", u, torch.float32)
+    _cuda("state", state, torch.float32)
+    _cuda("out", out, torch.float32, contiguous=False)
+    T = r.shape[0]
+    n = r.shape[1] // heads
+    R = low.shape[1]
+    D = h.shape[1]
+    if n > WKV_MAX_DIM or r.shape[1] != heads * n or tuple(k.shape) != tuple(r.shape) or tuple(v.shape) != tuple(r.shape) \
+            or tuple(out.shape) != tuple(r.shape) or tuple(w2.shape) != (heads * n, R) or w0.numel() != heads * n \
+            or u.numel() != heads * n or low.shape[0] != T or h.shape[0] != T or state.dim() != 2 \
+            or state.shape[1] < max(heads * n * n, prev_off + D) or prev_off < heads * n * n:
+        raise KernelError("wkv_scan: shapes do not fit")
+    _call("mllm_wkv_scan", r.data_ptr(), _rows("r", r), k.data_ptr(), _rows("k", k), v.data_ptr(), _rows("v", v),
+          low.data_ptr(), _rows("low", low), w2.data_ptr(), w0.data_ptr(), u.data_ptr(), h.data_ptr(), _rows("h", h),
+          state.data_ptr(), state.stride(0), int(prev_off), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(),
+          _rows("out", out), ctx.S, int(heads), n, R, D, int(write_state), _dt(r), _stream())
+
+
+def wkv_finish(o, z, weight, out, *, heads: int, eps: float) -> None:
+    """out = o / sqrt(mean(o^2) + eps) (per head) * weight * silu(z): o float32 [T, heads * n], z and out [T, heads * n] in
+    the activation dtype, weight float32 [heads * n]."""
+    _cuda("o", o, torch.float32, contiguous=False)
+    _cuda("z", z, contiguous=False)
+    _cuda("weight", weight, torch.float32)
+    _cuda("out", out, z.dtype, contiguous=False)
+    T, W = o.shape
+    if W % heads or tuple(z.shape) != (T, W) or tuple(out.shape) != (T, W) or weight.numel() != W:
+        raise KernelError("wkv_finish: shapes do not fit")
+    _call("mllm_wkv_finish", o.data_ptr(), _rows("o", o), z.data_ptr(), _rows("z", z), weight.data_ptr(), out.data_ptr(),
+          _rows("out", out), T, int(heads), W // heads, float(eps), _dt(z), _stream())
 
 
 # --------------------------------------------------------------------------- attention over a cache of latents
@@ -1222,11 +1350,13 @@ _moe_few_tokens = None
 
 
 def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int = 1, keep: int = 1, bias=None,
-              mode: str = "softmax_all") -> None:
+              mode: str = "softmax_all", group_sum: int = 1, weight_scale: float = 1.0) -> None:
     """Per row of h: softmax of the router's logits (32-bit) over all experts; the best ``keep`` of ``groups`` equal
     groups of neighbours (by their largest score); the ``top`` best experts within them -> idx [T, top] (int32) and
     weights [T, top] (scores over their sum + 1e-20).  ``bias`` (float32 [E]) is added to the logits first.  ``mode``
-    "softmax_top": the ``top`` largest logits are chosen and weighted by the softmax over those alone (no groups).
+    "softmax_top": the ``top`` largest logits are chosen and weighted by the softmax over those alone (no groups);
+    "sigmoid": the scores are sigmoid(logit), expert by expert.  ``group_sum`` 2: a group's score is the sum of its two
+    largest scores.  The weights are multiplied by ``weight_scale``.
     Then the (row, choice) pairs ordered by expert: offsets [E + 1], order [T * top]."""
     _cuda("h", h, contiguous=False)
     _cuda("router", router, h.dtype)
@@ -1242,10 +1372,11 @@ def moe_route(h, router, idx, weights, offsets, order, *, top: int, groups: int 
         _cuda("bias", bias, torch.float32)
         if bias.numel() != E:
             raise KernelError("moe_route: one bias per expert")
-    if mode not in ("softmax_all", "softmax_top"):
+    modes = {"softmax_all": 0, "softmax_top": 1, "sigmoid": 2}
+    if mode not in modes:
         raise KernelError(f"moe_route: unknown mode {mode!r}")
     _call("mllm_moe_route", h.data_ptr(), _rows("h", h), router.data_ptr(), bias.data_ptr() if bias is not None else None,
-          int(mode == "softmax_top"), T, D, E, int(top), int(groups), int(keep),
+          modes[mode], T, D, E, int(top), int(groups), int(keep), int(group_sum), float(weight_scale),
           idx.data_ptr(), weights.data_ptr(), offsets.data_ptr(), order.data_ptr(), _dt(h), _stream())
     global launches, _moe_few_tokens
     if _moe_few_tokens is None:
@@ -1258,23 +1389,26 @@ def moe_grouped(a, weight, out, offsets, order, *, top: int, first: bool, act: s
                 alpha: float = 1.0) -> None:
     """The experts' products over the pairs in ``order``.  ``first``: a [T, K] (row = pair // top), weight [E, 2F, K]
     (gate rows, then up rows) -> out[i] = silu(gate) * up (``act`` "swiglu_clamp": the clamped form of gated_act, with
-    ``limit`` and ``alpha``) for the i-th pair in order, [T*top, F].  Otherwise: a [T*top, K]
+    ``limit`` and ``alpha``) for the i-th pair in order, [T*top, F]; ``act`` "relu_sq": experts without a gate, weight
+    [E, F, K], out[i] = relu(.)^2.  Otherwise: a [T*top, K]
     in that order, weight [E, N, K] -> out[pair] [T*top, N] 32-bit, by pair id."""
     _cuda("a", a, contiguous=False)
     _cuda("weight", weight, a.dtype)
     _cuda("out", out, contiguous=False)
     E, rows, K = weight.shape
     n_pairs = order.numel()
-    N = rows // 2 if first else rows
+    ungated = first and act in _UNGATED_ACT
+    N = rows // 2 if (first and not ungated) else rows
     if a.shape[1] != K or tuple(out.shape) != (n_pairs, N) or offsets.numel() != E + 1:
         raise KernelError("moe_grouped: shapes do not fit")
-    if act not in ("silu", "swiglu_clamp") or (act == "swiglu_clamp" and not limit > 0):
+    if act not in ("silu", "swiglu_clamp", *_UNGATED_ACT) or (act == "swiglu_clamp" and not limit > 0):
         raise KernelError(f"moe_grouped: activation {act!r} (limit {limit})")
     if (first and out.dtype != a.dtype) or (not first and out.dtype != torch.float32):
         raise KernelError("moe_grouped: the first product keeps the dtype, the second gives 32-bit")
     _call("mllm_moe_grouped", a.data_ptr(), _rows("a", a), weight.data_ptr(), out.data_ptr(), _rows("out", out),
           offsets.data_ptr(), order.data_ptr(), n_pairs, E, N, K, int(top) if first else 0, 0 if first else 1,
-          0 if first else 1, _GATE_ACT[act], float(limit), float(alpha), _dt(a), _stream())
+          (2 if ungated else 0) if first else 1, _UNGATED_ACT[act] if ungated else _GATE_ACT[act], float(limit), float(alpha),
+          _dt(a), _stream())
 
 
 def moe_combine(pair_out, weights, y, *, top: int, accumulate: bool) -> None:

@@ -194,6 +194,15 @@ class RotaryAttention(ProjectedMixer):
     * ``sink``: a trained scalar s_h per head; exp(s_h) is one more term of the softmax's denominator and of nothing else,
       so part of a head's weight can go nowhere.
 
+    Further options, all constructor constants.  ``head_norm`` (instead of ``qk_norm``): after the rotation every query
+    head and every key head is divided by its own root mean square (no weights).  ``rot_scaling``: the frequencies'
+    scaling (``parts.rotary``).  ``bias``: the three projections have biases.  ``softcap`` c: the scaled product s becomes
+    c * tanh(s / c).  ``distance_slopes``: slope_h * (i - j) is taken off the score of query i and key j (after the cap),
+    slope_h = 2^(-8 (h + 1) / H).  ``value_mix``: "first": the values of the step's tokens are also kept in a buffer of
+    the step (``value_mix_key`` names it) for later layers; "mix": the values become (1 - lambda) v + lambda v_first
+    before they are cached, v_first that buffer's rows of the same tokens and lambda a trained scalar (``v_mix``; a
+    "first" layer has the tensor too and does not use it).
+
     The keys are cached normed and rotated (rows padded to 16-byte pieces), so a cached token is never touched again.
     With a chunk mask the pages of finished blocks go back to the pool as the request moves on.
     """
@@ -203,11 +212,26 @@ class RotaryAttention(ProjectedMixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float,
                  norm_eps: float = 1e-6, qk_norm: bool = True, rot_dims: int = 0, rot_base: float = 10000.0,
-                 rot_interleaved: bool = True, window: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False):
+                 rot_interleaved: bool = True, window: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False,
+                 head_norm: bool = False, rot_scaling: Optional[dict] = None, bias: bool = False,
+                 softcap: Optional[float] = None, distance_slopes: bool = False, value_mix: Optional[str] = None,
+                 value_mix_key: str = "v_first"):
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
         self.scale, self.norm_eps = float(scale), float(norm_eps)
         self.qk_norm = bool(qk_norm)
+        self.head_norm = bool(head_norm)
+        if self.qk_norm and self.head_norm:
+            raise ValueError("rotary attention: a norm over the whole projection or one per head, not both")
+        self.rot_scaling = None if rot_scaling is None else dict(rot_scaling)
+        self.has_bias = bool(bias)
+        self.softcap = None if softcap is None else float(softcap)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"rotary attention: the cap on the scores must be positive, got {softcap!r}")
+        self.distance_slopes = bool(distance_slopes)
+        if value_mix not in (None, "first", "mix"):
+            raise ValueError(f"rotary attention: value_mix is None, 'first' or 'mix', got {value_mix!r}")
+        self.value_mix, self.value_mix_key = value_mix, str(value_mix_key)
         self.rot_dims, self.rot_base, self.rot_interleaved = int(rot_dims), float(rot_base), bool(rot_interleaved)
         self.window = None if window is None else int(window)
         self.chunk = None if chunk is None else int(chunk)
@@ -222,13 +246,19 @@ class RotaryAttention(ProjectedMixer):
         self.k_size = self.num_kv_heads * self.head_dim
         self.v_size = self.num_kv_heads * self.v_head_dim
         self.k_row = -(-self.head_dim // 8) * 8        # a key row in the pages: padded to 16-byte pieces, the padding zero
-        self.q_norm = self.k_norm = self.sink = self.freq = None
+        self.q_norm = self.k_norm = self.sink = self.freq = self.slopes = self.v_mix = None
 
     def param_specs(self):
         p = {"q_weight": ParamSpec((self.q_size, self.hidden_size), "matrix"),
              "k_weight": ParamSpec((self.k_size, self.hidden_size), "matrix"),
              "v_weight": ParamSpec((self.v_size, self.hidden_size), "matrix"),
              "out_weight": ParamSpec((self.hidden_size, self.num_heads * self.v_head_dim), "matrix")}
+        if self.has_bias:
+            p["q_bias"] = ParamSpec((self.q_size,), "vector")
+            p["k_bias"] = ParamSpec((self.k_size,), "vector")
+            p["v_bias"] = ParamSpec((self.v_size,), "vector")
+        if self.value_mix is not None:
+            p["v_mix"] = ParamSpec((), "vector")
         if self.qk_norm:
             p["q_norm"] = ParamSpec((self.q_size,), "vector")
             p["k_norm"] = ParamSpec((self.k_size,), "vector")
@@ -242,7 +272,7 @@ class RotaryAttention(ProjectedMixer):
             out.append(f"rotary attention: key size {self.head_dim} is not between 1 and 256")
         if not (1 <= self.v_head_dim <= 256):
             out.append(f"rotary attention: value size {self.v_head_dim} is not between 1 and 256")
-        if (self.q_size + self.k_size) * 4 > 200 * 1024:
+        if (self.q_size + self.k_size) * 4 * (2 if self.head_norm else 1) > 200 * 1024:
             out.append(f"rotary attention: a token's {self.q_size} + {self.k_size} query and key entries do not fit the "
                        f"shared memory of the kernel that norms and rotates them")
         return out
@@ -258,20 +288,35 @@ class RotaryAttention(ProjectedMixer):
         if not params:
             return
         if self.rot_dims:
-            f, _ = rotary_table(self.rot_dims, self.rot_base)       # float64 -> float32; the kernel takes position * f in 32-bit
+            f, _ = rotary_table(self.rot_dims, self.rot_base, self.rot_scaling)   # float64 -> float32; the kernel takes position * f in 32-bit
             self.freq = torch.tensor(f, dtype=torch.float64).float().contiguous().to(rt.device)
+        if self.has_bias:
+            self.in_bias = torch.cat([self.q_bias, self.k_bias, self.v_bias]).contiguous()
+        if self.distance_slopes:
+            H = self.num_heads
+            self.slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float64).float().to(rt.device)
+        if self.value_mix is not None:
+            self.v_mix = self.v_mix.reshape(1).contiguous()
 
     def core(self, proj, ctx, cache, out, out_scale: float = 1.0) -> None:
         ops = self.rt.ops
         gv = ctx.groups[cache.group]
-        q = ctx.ws.buf("attn_q", proj.shape[0], self.q_size, self.rt.act_dtype)
+        T = proj.shape[0]
+        q = ctx.ws.buf("attn_q", T, self.q_size, self.rt.act_dtype)
+        mix = {}
+        if self.value_mix is not None:
+            # the first value-mixing layer's values of the step's tokens live in a buffer of the step under a name of
+            # their own: nothing else writes it between that layer and the ones that mix them in
+            kept = ctx.ws.buf("values_" + self.value_mix_key, T, self.v_size, self.rt.act_dtype)
+            mix = dict(v_keep=kept) if self.value_mix == "first" else dict(v_first=kept, v_lambda=self.v_mix)
         ops.qk_norm_rope(proj, 0, self.q_size, self.q_size + self.k_size, ctx, q, cache.k_pages, cache.v_pages,
                          gv.slot_mapping if cache.write else None, heads=self.num_heads, kv_heads=self.num_kv_heads,
                          head_dim=self.head_dim, v_head_dim=self.v_head_dim, q_norm=self.q_norm, k_norm=self.k_norm,
-                         eps=self.norm_eps, freq=self.freq, rot_dims=self.rot_dims, interleaved=self.rot_interleaved)
+                         eps=self.norm_eps, freq=self.freq, rot_dims=self.rot_dims, interleaved=self.rot_interleaved,
+                         head_norm=self.head_norm, **mix)
         ops.biased_attention(q, cache.k_pages, cache.v_pages, gv.block_table, ctx, out, num_heads=self.num_heads,
                              num_kv_heads=self.num_kv_heads, scale=self.scale, out_scale=out_scale, window=self.window,
-                             chunk=self.chunk, sink=self.sink)
+                             chunk=self.chunk, sink=self.sink, softcap=self.softcap or 0.0, slopes=self.slopes)
 
 
 register_part("mixer", "rotary_attention", RotaryAttention)

@@ -34,7 +34,8 @@ from typing import Any, Callable, Dict, Optional, Tuple
 @dataclass
 class ParamSpec:
     """``role``: "matrix" and "table" follow the engine dtype (bfloat16 or
-    float32); "vector" (norm weights, biases) is always float32; "int" is int32."""
+    float32); "vector" (norm weights, biases) is always float32; "int" is int32.  A size of ``shape`` that is None is
+    taken from the checkpoint as it is stored (a rank that the configuration does not name)."""
 
     shape: Tuple[int, ...]
     role: str = "matrix"

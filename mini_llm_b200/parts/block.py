@@ -5,6 +5,8 @@ x += mixer(norm(x)); x += ff(norm(x)), with the residual stream x in 32-bit.
 "parallel": x += mixer(norm_a(x)) + ff(norm_b(x)), both branches reading the same x.
 "sandwich": x = join_a(x, mixer(norm_a(x))); x = join_b(x, ff(norm_b(x))): a branch's result goes through the layer's
 join (a second norm and a scale per column, say) before it reaches x.
+"post_norm": x = norm_a(alpha * x + mixer(x)); x = norm_b(alpha * x + ff(x)): the branches read x itself and the norm
+comes after the sum (the joins are ``parts.join.PostNormJoin``); the layer has no norms in front of its branches.
 """
 from __future__ import annotations
 
@@ -96,3 +98,46 @@ def sandwich(layer, x, ctx, cache):
 
 
 register_part("arrangement", "sandwich", lambda: sandwich)
+
+
+def post_norm(layer, x, ctx, cache):
+    """x <- join_a(x, mixer(x)); x <- join_b(x, ff(x)) with joins that norm after the sum.  A branch reads x as the
+    products take it (the activation dtype): the copy that the join before it made (``ctx.carry``: the embedding's norm
+    or the layer before left it there), or x itself on the 32-bit path."""
+    import torch
+    if layer.mixer_join is None or (layer.ff is not None and layer.ff_join is None):
+        raise RuntimeError("post_norm arrangement: the layer has no join for a branch")
+    h = _take_act_copy(ctx, x, layer.mixer.rt.act_dtype)
+    y = ctx.ws.buf("branch_out", x.shape[0], x.shape[1], torch.float32)
+    _branch(layer.mixer, y, h, ctx, cache)
+    h = layer.mixer_join.forward(y, x, ctx)
+    if layer.ff is not None:
+        if hasattr(layer.ff, "forward_pairs") and getattr(layer.ff_join, "takes_pairs", False):
+            shared, pairs = layer.ff.forward_pairs(h, ctx, y)
+            h = layer.ff_join.forward(y if shared else None, x, ctx, pairs=pairs)
+        else:
+            _branch(layer.ff, y, h, ctx)
+            h = layer.ff_join.forward(y, x, ctx)
+    leave_act_copy(ctx, x, h)
+    return x
+
+
+def leave_act_copy(ctx, x, h) -> None:
+    """Whoever has just written the residual x leaves its copy in the activation dtype for the next reader."""
+    if hasattr(ctx, "carry"):
+        ctx.carry = ("act_copy", x, h)
+
+
+def _take_act_copy(ctx, x, act_dtype):
+    """The copy of x in the activation dtype that the last writer of x left, or one made now."""
+    left = getattr(ctx, "carry", None)
+    if isinstance(left, tuple) and len(left) == 3 and left[0] == "act_copy" and left[1].data_ptr() == x.data_ptr():
+        ctx.carry = None
+        return left[2]
+    if x.dtype == act_dtype:
+        return x
+    raise RuntimeError("post_norm arrangement: nobody left a copy of the residual in the activation dtype "
+                       "(the embedding of such a model norms its rows and leaves one)")
+
+
+register_part("arrangement", "post_norm", lambda: post_norm)

@@ -2,6 +2,9 @@
 
 ``NormScaleJoin``: x += rms_norm(y, w) * s, the branch's result normed once more (plain weights, eps inside the
 root) and multiplied column by column by a learned scale before it is added; all 32-bit, one kernel.
+
+``PostNormJoin``: x <- rms_norm(alpha * x + y, w), the block that norms after the sum; the new x also comes back in the
+activation dtype for the branch that reads it next; all 32-bit, one kernel.
 """
 from __future__ import annotations
 
@@ -42,3 +45,33 @@ class NormScaleJoin(Join):
 
 
 register_part("join", "norm_scale", NormScaleJoin)
+
+
+class PostNormJoin(Join):
+    takes_pairs = True      # forward(..., pairs=) takes the weighted sum over a routed feed-forward's choices itself
+
+    def __init__(self, hidden_size: int, eps: float, alpha: float = 1.0):
+        self.hidden_size = int(hidden_size)
+        self.eps = float(eps)
+        self.alpha = float(alpha)
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.hidden_size,), "vector")}
+
+    def forward(self, y, x, ctx, pairs=None):
+        """x <- n(alpha * x + y [+ the weighted pairs], w) in place; returns the new x as the products read it: x itself
+        on the 32-bit path, a copy in the activation dtype otherwise.  ``pairs``: (results [T * top, D], weights [T, top],
+        top) of a routed feed-forward whose weighted sum has not been taken yet (y may then be None); y None and no pairs:
+        the norm of alpha * x alone."""
+        import torch
+        kw = {}
+        if pairs is not None:
+            kw.update(pairs=pairs[0], pair_weights=pairs[1], top=pairs[2])
+        h = None
+        if self.rt.act_dtype != torch.float32:
+            h = ctx.ws.buf("post_norm_out", x.shape[0], self.hidden_size, self.rt.act_dtype)
+        self.rt.ops.post_norm(x, self.weight, self.eps, self.alpha, y=y, h=h, **kw)
+        return x if h is None else h
+
+
+register_part("join", "post_norm", PostNormJoin)

@@ -36,9 +36,9 @@ class LayerCache:
 class Layer:
     def __init__(self, spec, hidden_size):
         self.spec = spec
-        self.mixer_norm = build_part("norm", spec.mixer_norm)
+        self.mixer_norm = build_part("norm", spec.mixer_norm) if spec.mixer_norm is not None else None
         self.mixer = build_part("mixer", spec.mixer)
-        self.ff_norm = build_part("norm", spec.ff_norm) if spec.ff is not None else None
+        self.ff_norm = build_part("norm", spec.ff_norm) if (spec.ff is not None and spec.ff_norm is not None) else None
         self.ff = build_part("feed_forward", spec.ff) if spec.ff is not None else None
         self.mixer_join = build_part("join", spec.mixer_join) if spec.mixer_join is not None else None
         self.ff_join = build_part("join", spec.ff_join) if (spec.ff is not None and spec.ff_join is not None) else None

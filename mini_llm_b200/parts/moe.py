@@ -11,7 +11,9 @@ Variants, all constructor constants.  ``router_bias``: the logits get a trained 
 ``selection`` "softmax_top": no softmax over all experts; the ``top`` largest logits are chosen and weighted by the
 softmax over those alone (no groups).  ``activation`` "swiglu_clamp": an expert is W_down (g * sigmoid(alpha * g) *
 (u + 1)) with g = min(W_gate h, limit) and u = clamp(W_up h, -limit, limit); the shared expert has a limit of its own
-(``shared_limit``).
+(``shared_limit``).  ``selection`` "sigmoid": the scores are sigmoid(z), expert by expert; ``group_sum`` 2: a group's
+score is the sum of its two largest scores; ``weight_scale``: a factor on the weights.  ``activation`` "relu_sq": an
+expert has no gate, W_down relu(W_up h)^2.
 
 Nothing is read back by the host: a kernel routes and orders the (token, choice) pairs by expert, and the experts'
 products run over that order with a grid that depends on the number of pairs only, so the step can be captured in a
@@ -30,20 +32,26 @@ class MoEFeedForward(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, groups: int = 1, keep: int = 1,
                  shared_size: Optional[int] = None, activation: str = "silu", router_bias: bool = False,
                  selection: str = "softmax_all", limit: float = 0.0, alpha: float = 1.0,
-                 shared_limit: Optional[float] = None):
+                 shared_limit: Optional[float] = None, group_sum: int = 1, weight_scale: float = 1.0):
         self.hidden_size, self.num_experts, self.top = int(hidden_size), int(num_experts), int(top)
         self.expert_size, self.groups, self.keep = int(expert_size), int(groups), int(keep)
         self.shared_size = None if shared_size is None else int(shared_size)
-        if activation not in ("silu", "swiglu_clamp"):
-            raise ValueError(f"MoEFeedForward: the experts' activation is silu or swiglu_clamp, got {activation!r}")
+        if activation not in ("silu", "swiglu_clamp", "relu_sq"):
+            raise ValueError(f"MoEFeedForward: the experts' activation is silu, swiglu_clamp or relu_sq, got {activation!r}")
         self.activation = activation
+        self.gated = activation != "relu_sq"
+        if not self.gated and self.shared_size is not None:
+            raise ValueError("MoEFeedForward: experts without a gate come without a shared expert")
+        self.group_sum, self.weight_scale = int(group_sum), float(weight_scale)
+        if self.group_sum not in (1, 2):
+            raise ValueError(f"MoEFeedForward: a group's score is its largest score or the sum of its two largest, got {group_sum!r}")
         self.limit, self.alpha = float(limit), float(alpha)
         self.shared_limit = self.limit if shared_limit is None else float(shared_limit)
         if activation == "swiglu_clamp" and not (self.limit > 0 and self.shared_limit > 0):
             raise ValueError("MoEFeedForward: the clamped activation needs positive limits")
         self.has_router_bias = bool(router_bias)
-        if selection not in ("softmax_all", "softmax_top"):
-            raise ValueError(f"MoEFeedForward: selection is softmax_all or softmax_top, got {selection!r}")
+        if selection not in ("softmax_all", "softmax_top", "sigmoid"):
+            raise ValueError(f"MoEFeedForward: selection is softmax_all, softmax_top or sigmoid, got {selection!r}")
         if selection == "softmax_top" and self.groups != 1:
             raise ValueError("MoEFeedForward: the softmax over the chosen logits takes no groups")
         self.selection = selection
@@ -59,7 +67,8 @@ class MoEFeedForward(FeedForward):
         if self.has_router_bias:
             p["router_bias"] = ParamSpec((self.num_experts,), "vector")
         for e in range(self.num_experts):
-            p[f"expert{e}.gate"] = ParamSpec((F, D), "matrix")
+            if self.gated:
+                p[f"expert{e}.gate"] = ParamSpec((F, D), "matrix")
             p[f"expert{e}.up"] = ParamSpec((F, D), "matrix")
             p[f"expert{e}.down"] = ParamSpec((D, F), "matrix")
         if self.shared_size is not None:
@@ -83,7 +92,10 @@ class MoEFeedForward(FeedForward):
         E = self.num_experts
         self.router = params["router"]
         self.router_bias = params.get("router_bias")
-        self.w_first = torch.stack([torch.cat([params[f"expert{e}.gate"], params[f"expert{e}.up"]], 0) for e in range(E)]).contiguous()
+        if self.gated:
+            self.w_first = torch.stack([torch.cat([params[f"expert{e}.gate"], params[f"expert{e}.up"]], 0) for e in range(E)]).contiguous()
+        else:
+            self.w_first = torch.stack([params[f"expert{e}.up"] for e in range(E)]).contiguous()
         self.w_second = torch.stack([params[f"expert{e}.down"] for e in range(E)]).contiguous()
         if self.shared_size is not None:
             self.shared_first = torch.cat([params["shared.gate"], params["shared.up"]], 0).contiguous()
@@ -99,7 +111,7 @@ class MoEFeedForward(FeedForward):
         order = ctx.ws.buf("moe_order", T, top, torch.int32)
         offsets = ctx.ws.buf("moe_offsets", 1, E + 1, torch.int32)
         ops.moe_route(h, self.router, idx, wts, offsets, order, top=top, groups=self.groups, keep=self.keep,
-                      bias=self.router_bias, mode=self.selection)
+                      bias=self.router_bias, mode=self.selection, group_sum=self.group_sum, weight_scale=self.weight_scale)
         mid = ctx.ws.buf("moe_mid", T * top, self.expert_size, self.rt.act_dtype)
         ops.moe_grouped(h, self.w_first, mid, offsets, order, top=top, first=True, act=self.activation, limit=self.limit,
                         alpha=self.alpha)

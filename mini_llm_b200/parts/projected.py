@@ -28,6 +28,7 @@ class ProjectedMixer(Mixer):
     can_overwrite = True                # forward(..., accumulate=False) writes the result instead of adding it
     in_names: Sequence[str] = ()        # parameters stacked (by rows) into the input projection, in this order
     out_name: str = "out_weight"        # the output projection [hidden, core_width]
+    in_bias = None                      # a bias on the input projection (float32 [in_width]), set at bind by a mixer that has one
 
     @property
     def in_width(self) -> int:
@@ -52,7 +53,7 @@ class ProjectedMixer(Mixer):
         T = h.shape[0]
         n_in = self.in_weight.shape[0]
         proj = ctx.ws.buf("mix_proj", T, -(-n_in // 8) * 8, self.rt.act_dtype)[:, :n_in]    # rows stay 16-byte aligned
-        ops.linear(h, self.in_weight, None, out=proj)
+        ops.linear(h, self.in_weight, self.in_bias, out=proj)
         mid = ctx.ws.buf("mix_core", T, self.core_width, self.rt.act_dtype)
         self.core(proj, ctx, cache, mid)
         ops.linear(mid, getattr(self, self.out_name), None, out=out_accum, accumulate=accumulate)

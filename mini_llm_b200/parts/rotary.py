@@ -9,6 +9,11 @@ d(t) = dims * ln(original / (2 pi t)) / (2 ln base); with lo = max(floor(d(fast)
 and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i * (1 - ramp_i),
 and cos and sin are multiplied by 0.1 * ln(factor) + 1.  The kernels take the table (float32) and the factor; they
 compute the angle, cos and sin in 32-bit at the token's position.
+
+Scaling by wavelength (``scaling`` = {factor, low, high, original}; the form Llama 3.1 uses): a pair whose wavelength
+l_i = 2 pi / f_i is shorter than original / high keeps its frequency, one longer than original / low turns ``factor``
+times slower, and between the two the frequency is (1 - s) f_i / factor + s f_i with s = (original / l_i - low) /
+(high - low); cos and sin keep their size.
 """
 from __future__ import annotations
 
@@ -25,6 +30,21 @@ def rotary_table(dims: int, base: float, scaling: Optional[dict] = None) -> Tupl
     if not scaling:
         return f, 1.0
     factor, orig = float(scaling["factor"]), float(scaling["original"])
+    if "low" in scaling or "high" in scaling:
+        low, high = float(scaling["low"]), float(scaling["high"])
+        if not (high > low > 0 and factor > 0 and orig > 0):
+            raise ValueError(f"rotary: scaling by wavelength needs high > low > 0 and positive factor and original, got {scaling!r}")
+        scaled = []
+        for fi in f:
+            turns = orig * fi / (2.0 * math.pi)          # original / wavelength: turns over the original context
+            if turns > high:
+                scaled.append(fi)
+            elif turns < low:
+                scaled.append(fi / factor)
+            else:
+                s = (turns - low) / (high - low)
+                scaled.append((1.0 - s) * fi / factor + s * fi)
+        return scaled, 1.0
 
     def at(turns: float) -> float:
         return dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))

@@ -58,7 +58,7 @@ class LayerSpec:
 
     mixer: PartSpec
     ff: Optional[PartSpec]
-    mixer_norm: PartSpec
+    mixer_norm: Optional[PartSpec]      # None (with ``ff_norm`` None): the arrangement norms after the sum, in its joins
     ff_norm: Optional[PartSpec]
     arrangement: str = "pre_norm"
     mixer_join: Optional[PartSpec] = None
@@ -121,12 +121,14 @@ class ModelSpec:
         yield "embedding", self.embedding
         yield "positions", self.positions
         for i, l in enumerate(self.layers):
-            yield f"layers.{i}.mixer_norm", l.mixer_norm
+            if l.mixer_norm is not None:
+                yield f"layers.{i}.mixer_norm", l.mixer_norm
             yield f"layers.{i}.mixer", l.mixer
             if l.mixer_join is not None:
                 yield f"layers.{i}.mixer_join", l.mixer_join
             if l.ff is not None:
-                yield f"layers.{i}.ff_norm", l.ff_norm
+                if l.ff_norm is not None:
+                    yield f"layers.{i}.ff_norm", l.ff_norm
                 yield f"layers.{i}.ff", l.ff
                 if l.ff_join is not None:
                     yield f"layers.{i}.ff_join", l.ff_join

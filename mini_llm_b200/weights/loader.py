@@ -86,7 +86,7 @@ def load_weights(model, spec: ModelSpec, model_dir: str, rt) -> None:
                 used.add(found)
                 exp = checkpoint_shape(wanted[local].shape, ref)
                 got = sf.shape(found)
-                if tuple(got) != tuple(exp):
+                if len(got) != len(exp) or any(e is not None and e != g for g, e in zip(got, exp)):     # None: as stored
                     wrong.append((found, exp, got))
                     continue
                 if not (sf.dtype(found).is_floating_point or wanted[local].role == "int"):

@@ -32,6 +32,9 @@ def random_tensors(spec, model, seed: int, dtype: torch.dtype = torch.float32):
         wanted = part.param_specs()
         for local, ref in pspec.weights.items():
             shape = checkpoint_shape(wanted[local].shape, ref)
+            if any(n is None for n in shape):
+                raise ValueError(f"{ref.canonical}: the configuration leaves a size of this tensor to the checkpoint; "
+                                 f"random weights need it given")
             kind = ref.init[0]
             if kind == "normal":
                 t = torch.empty(shape, dtype=torch.float32).normal_(0.0, float(ref.init[1]), generator=gen)
