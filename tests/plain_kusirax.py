@@ -147,9 +147,10 @@ def token_shift(h, mu, h_before=None):
 
 
 def decay(xw, w1, w2, w0, store: Callable = _keep):
-    """exp(-exp(W2 tanh(W1 xw) + w0)) per channel."""
-    low = store(torch.tanh(store(xw @ w1.T)))
-    return torch.exp(-torch.exp(store(low @ w2.T) + w0))
+    """exp(-exp(W2 tanh(W1 xw) + w0)) per channel.  Only the first product's result is handed on in the activation
+    dtype; from the tanh on everything belongs to the recurrence and stays exact."""
+    low = torch.tanh(store(xw @ w1.T))
+    return torch.exp(-torch.exp(low @ w2.T + w0))
 
 
 def wkv_scan(r, k, v, w, u, S0=None):
