@@ -40,7 +40,7 @@ with "impl": "reference" and "dtype": "fp32".  The reference holds at most 16 re
 (more are cut) and there is no batch-64 point.  Where it cannot be built or run the line is
 {"impl": "reference", "unavailable": "<why>"}.
 
-``--compare-designs [small,medium,large]`` measures the engine's other designs, Finuvik, Falisun and Mumopel, beside
+``--compare-designs [small,medium,large]`` measures the engine's other designs, Finuvik, Falisun, Mumopel and Kusirax, beside
 GPT-2 at equal width, depth and head count (bfloat16 unless --dtype is given; ``--designs gpt2,falisun`` picks some).
 
 ``--profile-step prefill|decode [--kernel-times]`` runs one small eager step (for a profiler, or to
@@ -316,7 +316,7 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: b
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
 
     cfg = dict(SMALL, n_layer=layers)
-    if design in ("finuvik", "falisun", "mumopel"):  # the same step of the other designs at the "small" comparison size
+    if design in ("finuvik", "falisun", "mumopel", "kusirax"):  # the same step of the other designs at the "small" comparison size
         cfg = design_configs("small")[design]
         cfg["layers"] = cfg["layers"][:layers]
         cfg["n_positions"], cfg["vocab_size"] = DESIGN_POSITIONS, cfg["vocab"]      # the names used below
@@ -481,7 +481,28 @@ def design_configs(size: str):
     ml = [dict(type="attention", mixer=dict(attn), mlp=dict(kind="dense", ff=F) if i == 0 else routed) for i in range(L)]
     mumopel = dict(architecture="Mumopel", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), layers=ml, streams=2,
                    logit_softcap=30.0)
-    return {"gpt2": gpt2, "finuvik": finuvik, "falisun": falisun, "mumopel": mumopel}
+    # Kusirax at the same width, heads and key/value heads: recurrent layers (heads of 64 entries over the whole width, a
+    # decay of rank 64) around a rotary attention layer (half of every head turns, frequencies scaled by wavelength) and an
+    # attention_2 layer (biases, scores capped at 50, slopes, blocks of 768 positions), all attention layers mixing their
+    # values; dense feed-forwards of Finuvik's inner size alternate with 8 experts without gates in 4 groups of which 2
+    # are kept, two per token, of 3/8 of it (two matrices instead of three: as many weights per token as Mumopel's)
+    kinds = ["wkv", "attention", "attention_2", "wkv"]
+    kl = []
+    for i in range(L):
+        kind = kinds[i % len(kinds)]
+        if kind == "wkv":
+            mixer = dict(heads=D // 64, dim=64, decay_rank=64)
+        else:
+            mixer = dict(heads=H, kv_heads=z["kv_heads"], dim=dh, vdim=dh, scale=dh ** -0.5, v_mix=True)
+            if kind == "attention":
+                mixer["rot"] = dict(base=10000.0, dims=dh // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=512))
+            else:
+                mixer.update(mask=dict(size=768), softcap=50.0)
+        mlp = dict(kind="dense", ff=F) if i % 2 == 0 else \
+            dict(kind="moe", router=dict(experts=8, top=2, scale=2.5, groups=dict(count=4, keep=2)), expert=dict(ff=3 * F // 8 // 8 * 8))
+        kl.append(dict(type=kind, mixer=mixer, mlp=mlp))
+    kusirax = dict(architecture="Kusirax", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), postln_alpha=2.0, layers=kl)
+    return {"gpt2": gpt2, "finuvik": finuvik, "falisun": falisun, "mumopel": mumopel, "kusirax": kusirax}
 
 
 def _design_model(model_dir, dtype, batch, tokens):
@@ -744,7 +765,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64, prefill and other-precision measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
-    ap.add_argument("--design", choices=["gpt2", "finuvik", "falisun", "mumopel"], default="gpt2",
+    ap.add_argument("--design", choices=["gpt2", "finuvik", "falisun", "mumopel", "kusirax"], default="gpt2",
                     help="with --profile-step: the model whose step is run (the other designs: the 'small' size of --compare-designs)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --profile-step: time every launch of one eager step with CUDA events and print the shares")
@@ -755,7 +776,7 @@ def main() -> int:
     ap.add_argument("--compare-designs", nargs="?", const="small,medium,large", metavar="SIZES",
                     help="measure Finuvik, Falisun and Mumopel beside GPT-2 at equal sizes (a comma list of small, medium, large) "
                          "instead of the benchmark: prefill of 2 x 1024 tokens and decode at --batch, one JSON line per size")
-    ap.add_argument("--designs", default="", help="with --compare-designs: a comma list of gpt2, finuvik, falisun, mumopel (default: all)")
+    ap.add_argument("--designs", default="", help="with --compare-designs: a comma list of gpt2, finuvik, falisun, mumopel, kusirax (default: all)")
     args = ap.parse_args()
     if args.compare_designs:
         sizes = [z for z in args.compare_designs.split(",") if z]

@@ -10,9 +10,11 @@
 // to S, so that the next step finds it.  State, decay (tanh, both exponentials), the update, o, the norm and the gate
 // are 32-bit whatever the dtype of the projections.
 //
-// Three kernels.  `shift`: the mixes of every token (one CTA per token).  `scan`: a CTA takes 32 columns of one
+// Four kernels.  `shift`: the mixes of every token (one CTA per token).  `decay`: the decays of every token and channel,
+// off the recurrence's sequential path.  `scan`: a CTA takes 32 columns of one
 // (request, head)'s state; thread (lane, g) keeps rows g*WR .. g*WR+WR-1 of column lane in registers for the whole walk,
-// tokens come CH at a time (r, k, the decays and v staged in shared memory), the row groups' partial outputs meet in
+// tokens come CH at a time (r, k, the decays and v staged in shared memory, the next chunk's fetched into registers
+// meanwhile), the row groups' partial outputs meet in
 // group order; every element of the state is a recurrence of its own, so the state after n tokens is the same bits
 // however the tokens were cut into steps.  `finish`: one warp per (token, head): the unit norm, the weight and the gate.
 #include "common.cuh"
@@ -45,30 +47,69 @@ wkv_shift_kernel(const T* h, long long ldh, const float* __restrict__ mu, const 
     }
 }
 
+// w[t][c] = exp(-exp(w0[c] + sum_q W2[c][q] tanh(low[t][q]))): a CTA takes 16 tokens and 64 channels; the tokens' tanh
+// values are staged in shared memory, a thread keeps one channel's sums for four tokens.  Every token's sum runs over q in
+// the same order, whatever else is in the step.
+constexpr int DEC_TOK = 16, DEC_CH = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+wkv_decay_kernel(const T* low, long long l_stride, const T* __restrict__ W2, const float* __restrict__ w0, float* __restrict__ w,
+                 long long w_stride, int Tn, int N, int R) {
+    extern __shared__ float tl[];           // [DEC_TOK][R]
+    pdl_wait();
+    pdl_launch();
+    const int t0 = blockIdx.x * DEC_TOK, nt = min(DEC_TOK, Tn - t0);
+    for (int idx = threadIdx.x; idx < DEC_TOK * R; idx += blockDim.x) {
+        const int c = idx / R, q = idx % R;
+        tl[idx] = c < nt ? tanhf(to_f32(low[(size_t)(t0 + c) * l_stride + q])) : 0.f;
+    }
+    __syncthreads();
+    const int ch = blockIdx.y * DEC_CH + (threadIdx.x & (DEC_CH - 1)), tg = threadIdx.x / DEC_CH;     // tokens tg, tg + 4, ...
+    if (ch >= N) return;
+    const float b = w0[ch];
+    float acc[DEC_TOK / 4];
+#pragma unroll
+    for (int u = 0; u < DEC_TOK / 4; ++u) acc[u] = b;
+    const T* wr = W2 + (size_t)ch * R;
+#pragma unroll 8
+    for (int q = 0; q < R; ++q) {
+        const float wv = to_f32(wr[q]);
+#pragma unroll
+        for (int u = 0; u < DEC_TOK / 4; ++u) acc[u] = fmaf(wv, tl[(tg + 4 * u) * R + q], acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < DEC_TOK / 4; ++u) {
+        const int c = tg + 4 * u;
+        if (c < nt) w[(size_t)(t0 + c) * w_stride + ch] = expf(-expf(acc[u]));
+    }
+}
+
 struct WkvArgs {
     const int* cu_q;        // [S+1] first flat token of every request of the step
     const int* slots;       // [S] state slot of every request
-    const float* w0;        // [Hr*n]
     const float* u;         // [Hr*n]
     float* state;           // [slots][state_stride]: S of every head [Hr][n][n], then the last row of h at prev_off
     long long state_stride, prev_off;
-    long long r_stride, k_stride, v_stride, l_stride, o_stride, h_stride;
-    int Hr, n, R, D, write_state;
+    long long r_stride, k_stride, v_stride, w_stride, o_stride, h_stride;
+    int Hr, n, D, write_state;
 };
 
-// grid (requests, heads, ceil(n / 32)); block (32, G), G = ceil(n / WR).  o [T][Hr*n] float.
+// grid (requests, heads, ceil(n / 32)); block (32, G), G = ceil(n / WR).  o [T][Hr*n] float.  The next chunk's inputs
+// are fetched into registers while the current chunk is walked, so the walk never waits for global memory.
 template <typename T, int WR>
 __global__ void __launch_bounds__(1024)
-wkv_scan_kernel(const T* r, const T* k, const T* v, const T* low, const T* __restrict__ W2, const T* h, float* __restrict__ o,
-                WkvArgs a) {
+wkv_scan_kernel(const T* r, const T* k, const T* v, const float* w, const T* h, float* __restrict__ o, WkvArgs a) {
     extern __shared__ __align__(16) float sm[];
-    const int n = a.n, R = a.R, G = blockDim.y, np = G * WR;    // rows padded to a multiple of WR: the padding has r = k = 0, w = 1
+    constexpr int PF = WKV_CH * WR / 32;      // elements of r (and of k, of w) a thread fetches per chunk
+    constexpr int PFV = 2;                    // elements of v a thread fetches ahead (WKV_CH / G of them; with fewer than 8
+                                              // row groups, i.e. tiny heads, v is staged directly instead)
+    const int n = a.n, G = blockDim.y, np = G * WR;    // rows padded to a multiple of WR: the padding has r = k = 0, w = 1
     float* rs = sm;                           // [CH][np]
     float* ks = rs + WKV_CH * np;             // [CH][np]
     float* ws = ks + WKV_CH * np;             // [CH][np]
     float* vs = ws + WKV_CH * np;             // [CH][32]
-    float* tl = vs + WKV_CH * WKV_COLS;       // [CH][R]   tanh of the low-rank projection
-    float* os = tl + WKV_CH * R;              // [G][CH][32]
+    float* os = vs + WKV_CH * WKV_COLS;       // [G][CH][32]
     pdl_wait();
     pdl_launch();
     const int seq = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * WKV_COLS;
@@ -92,41 +133,65 @@ wkv_scan_kernel(const T* r, const T* k, const T* v, const T* low, const T* __res
         const T* last = h + (size_t)(t1 - 1) * a.h_stride;
         for (int d = tid; d < a.D; d += nthreads) kept[d] = to_f32(last[d]);
     }
+    // which elements of a chunk this thread fetches: the same in every chunk
+    int e_c[PF], e_i[PF];
+#pragma unroll
+    for (int x = 0; x < PF; ++x) {
+        const int idx = tid + x * nthreads;
+        e_c[x] = idx / np;
+        e_i[x] = idx % np;
+    }
+    const int vcount = (WKV_CH * WKV_COLS + nthreads - 1) / nthreads;
+    const bool v_ahead = vcount <= PFV;
+    float pr[PF], pk[PF], pw[PF], pv[PFV];
+    auto fetch = [&](int c0) {
+        const int nc = min(WKV_CH, t1 - c0);
+#pragma unroll
+        for (int x = 0; x < PF; ++x) {
+            pr[x] = 0.f; pk[x] = 0.f; pw[x] = 1.f;
+            if (e_c[x] < nc && e_i[x] < n) {
+                const size_t t = (size_t)(c0 + e_c[x]);
+                const size_t cix = (size_t)hd * n + e_i[x];
+                pr[x] = to_f32(r[t * a.r_stride + cix]);
+                pk[x] = to_f32(k[t * a.k_stride + cix]);
+                pw[x] = w[t * a.w_stride + cix];
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < PFV; ++x) {
+            pv[x] = 0.f;
+            if (v_ahead && x < vcount) {
+                const int idx = tid + x * nthreads, c = idx / WKV_COLS, d = idx % WKV_COLS;
+                if (idx < WKV_CH * WKV_COLS && c < nc && j0 + d < n)
+                    pv[x] = to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)hd * n + j0 + d]);
+            }
+        }
+    };
+    fetch(t0);
     for (int c0 = t0; c0 < t1; c0 += WKV_CH) {
         const int nc = min(WKV_CH, t1 - c0);
         __syncthreads();                      // the chunk before is no longer read
-        for (int idx = tid; idx < nc * R; idx += nthreads) {
-            const int c = idx / R, q = idx % R;
-            tl[c * R + q] = tanhf(to_f32(low[(size_t)(c0 + c) * a.l_stride + q]));
+#pragma unroll
+        for (int x = 0; x < PF; ++x) {
+            const int idx = tid + x * nthreads;
+            rs[idx] = pr[x];
+            ks[idx] = pk[x];
+            ws[idx] = pw[x];
         }
-        for (int idx = tid; idx < nc * np; idx += nthreads) {
-            const int c = idx / np, i = idx % np;
-            float rv = 0.f, kv = 0.f;
-            if (i < n) {
-                rv = to_f32(r[(size_t)(c0 + c) * a.r_stride + (size_t)hd * n + i]);
-                kv = to_f32(k[(size_t)(c0 + c) * a.k_stride + (size_t)hd * n + i]);
+        if (v_ahead) {
+#pragma unroll
+            for (int x = 0; x < PFV; ++x) {
+                const int idx = tid + x * nthreads;
+                if (x < vcount && idx < WKV_CH * WKV_COLS) vs[idx] = pv[x];
             }
-            rs[c * np + i] = rv;
-            ks[c * np + i] = kv;
-        }
-        for (int idx = tid; idx < nc * WKV_COLS; idx += nthreads) {
-            const int c = idx / WKV_COLS, d = idx % WKV_COLS;
-            vs[idx] = j0 + d < n ? to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)hd * n + j0 + d]) : 0.f;
+        } else {
+            for (int idx = tid; idx < WKV_CH * WKV_COLS; idx += nthreads) {
+                const int c = idx / WKV_COLS, d = idx % WKV_COLS;
+                vs[idx] = (c < nc && j0 + d < n) ? to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)hd * n + j0 + d]) : 0.f;
+            }
         }
         __syncthreads();
-        for (int idx = tid; idx < nc * np; idx += nthreads) {
-            const int c = idx / np, i = idx % np;
-            float w = 1.f;
-            if (i < n) {
-                float dot = a.w0[hd * n + i];
-                const T* wr = W2 + ((size_t)hd * n + i) * R;
-                const float* tc = tl + c * R;
-                for (int q = 0; q < R; ++q) dot = fmaf(to_f32(wr[q]), tc[q], dot);
-                w = expf(-expf(dot));
-            }
-            ws[c * np + i] = w;
-        }
-        __syncthreads();
+        if (c0 + WKV_CH < t1) fetch(c0 + WKV_CH);
         for (int c = 0; c < nc; ++c) {
             const float vj = vs[c * WKV_COLS + lane];
             const float* rr = rs + c * np + g * WR;
@@ -200,29 +265,52 @@ MLLM_EXPORT int mllm_wkv_shift(const void* h, long long ldh, const float* mu, co
     return 0;
 }
 
-// r, k, v [T, Hr*n], low [T, R], W2 [Hr*n, R] in `dtype`; w0, u [Hr*n] float; h [T, D] (its last row of every request is
+// low [T, R], W2 [N, R] in `dtype`; w0 [N] float; w [T, N] float = exp(-exp(W2 tanh(low) + w0)).
+MLLM_EXPORT int mllm_wkv_decay(const void* low, long long l_stride, const void* W2, const float* w0, float* w, long long w_stride,
+                               int T, int N, int R, int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (N <= 0 || R <= 0) return mllm_fail(1, "wkv_decay: %d channels, rank %d", N, R);
+    const size_t smem = sizeof(float) * (size_t)DEC_TOK * R;
+    if (smem > 96 * 1024) return mllm_fail(1, "wkv_decay: rank %d does not fit shared memory", R);
+    const dim3 grid((T + DEC_TOK - 1) / DEC_TOK, (N + DEC_CH - 1) / DEC_CH);
+    if (grid.y > 65535) return mllm_fail(1, "wkv_decay: too many channels");
+    if (dtype == MLLM_F32) {
+        if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(wkv_decay_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MLLM_CUDA(mllm_launch(wkv_decay_kernel<float>, grid, dim3(256), smem, stream, true, (const float*)low, l_stride,
+                              (const float*)W2, w0, w, w_stride, T, N, R));
+    } else if (dtype == MLLM_BF16) {
+        if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(wkv_decay_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MLLM_CUDA(mllm_launch(wkv_decay_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, true, (const __nv_bfloat16*)low,
+                              l_stride, (const __nv_bfloat16*)W2, w0, w, w_stride, T, N, R));
+    } else {
+        return mllm_fail(1, "wkv_decay: unknown dtype code %d", dtype);
+    }
+    return 0;
+}
+
+// r, k, v [T, Hr*n] in `dtype`; w [T, Hr*n] float (the decays); u [Hr*n] float; h [T, D] (its last row of every request is
 // kept); state [slots][state_stride] float with S at 0 and the kept row at prev_off; o [T, Hr*n] float.
 MLLM_EXPORT int mllm_wkv_scan(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
-                              long long v_stride, const void* low, long long l_stride, const void* W2, const float* w0,
-                              const float* u, const void* h, long long h_stride, float* state, long long state_stride,
-                              long long prev_off, const int* cu_q, const int* slots, float* o, long long o_stride, int S,
-                              int Hr, int n, int R, int D, int write_state, int dtype, cudaStream_t stream) {
+                              long long v_stride, const float* w, long long w_stride, const float* u, const void* h,
+                              long long h_stride, float* state, long long state_stride, long long prev_off, const int* cu_q,
+                              const int* slots, float* o, long long o_stride, int S, int Hr, int n, int D, int write_state,
+                              int dtype, cudaStream_t stream) {
     if (S <= 0) return 0;
-    if (Hr <= 0 || n <= 0 || n > 256 || R <= 0) return mllm_fail(1, "wkv_scan: %d heads of %d, rank %d", Hr, n, R);
+    if (Hr <= 0 || n <= 0 || n > 256) return mllm_fail(1, "wkv_scan: %d heads of %d", Hr, n);
     if (Hr > 65535) return mllm_fail(1, "wkv_scan: grid of %d x %d", S, Hr);
     const int WR = n <= 64 ? 2 : (n <= 128 ? 4 : 8);
     const int G = (n + WR - 1) / WR, np = G * WR;
-    const size_t smem = sizeof(float) * ((size_t)3 * WKV_CH * np + WKV_CH * WKV_COLS + (size_t)WKV_CH * R + (size_t)G * WKV_CH * WKV_COLS);
-    if (smem > 200 * 1024) return mllm_fail(1, "wkv_scan: heads of %d with rank %d need %zu bytes of shared memory", n, R, smem);
-    WkvArgs a{cu_q, slots, w0, u, state, state_stride, prev_off, r_stride, k_stride, v_stride, l_stride, o_stride, h_stride,
-              Hr, n, R, D, write_state};
+    const size_t smem = sizeof(float) * ((size_t)3 * WKV_CH * np + WKV_CH * WKV_COLS + (size_t)G * WKV_CH * WKV_COLS);
+    if (smem > 200 * 1024) return mllm_fail(1, "wkv_scan: heads of %d need %zu bytes of shared memory", n, smem);
+    WkvArgs a{cu_q, slots, u, state, state_stride, prev_off, r_stride, k_stride, v_stride, w_stride, o_stride, h_stride,
+              Hr, n, D, write_state};
     const dim3 grid(S, Hr, (n + WKV_COLS - 1) / WKV_COLS), block(32, G);
 #define MLLM_WKV(TT, WRR)                                                                                                \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
             MLLM_CUDA(cudaFuncSetAttribute(wkv_scan_kernel<TT, WRR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         MLLM_CUDA(mllm_launch(wkv_scan_kernel<TT, WRR>, grid, block, smem, stream, true, (const TT*)r, (const TT*)k,    \
-                              (const TT*)v, (const TT*)low, (const TT*)W2, (const TT*)h, o, a));                         \
+                              (const TT*)v, w, (const TT*)h, o, a));                                                     \
     } while (0)
     if (dtype == MLLM_F32) {
         if (WR == 2) MLLM_WKV(float, 2); else if (WR == 4) MLLM_WKV(float, 4); else MLLM_WKV(float, 8);

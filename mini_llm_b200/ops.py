@@ -107,9 +107,9 @@ def _signatures(lib):
                            c_int, c_float, c_int, c_void_p],
         "mllm_wkv_shift": [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_void_p],
-        "mllm_wkv_scan": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_ll, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_void_p],
+        "mllm_wkv_decay": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_wkv_scan": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p,
+                          c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_wkv_finish": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int,
                             c_void_p],
         "mllm_wkv_max_dim": [],
@@ -1126,32 +1126,45 @@ def wkv_shift(h, mu, state, prev_off: int, ctx, mixes) -> None:
           mixes.data_ptr(), T, D, NS, _dt(h), _stream())
 
 
-def wkv_scan(r, k, v, low, w2, w0, u, h, state, prev_off: int, ctx, out, *, heads: int, write_state: bool = True) -> None:
-    """The recurrence of csrc/wkv.cu over the step's tokens, request by request: w = exp(-exp(w2 tanh(low) + w0));
-    o = (S + diag(u) k v^T)^T r; S <- diag(w) S + k v^T.  r, k, v [T, heads * n], low [T, R], w2 [heads * n, R] in one
-    dtype; w0, u float32 [heads * n]; state float32 [slots, row] with S [heads, n, n] at column 0 and the last row of h
+def wkv_decay(low, w2, w0, out) -> None:
+    """out[t, c] = exp(-exp(w0[c] + sum_q w2[c, q] * tanh(low[t, q]))), 32-bit: the decays of csrc/wkv.cu's recurrence.
+    low [T, R] and w2 [N, R] in one dtype, w0 float32 [N], out float32 [T, N]."""
+    _cuda("low", low, contiguous=False)
+    _cuda("w2", w2, low.dtype)
+    _cuda("w0", w0, torch.float32)
+    _cuda("out", out, torch.float32, contiguous=False)
+    T, R = low.shape
+    N = w2.shape[0]
+    if tuple(w2.shape) != (N, R) or w0.numel() != N or tuple(out.shape) != (T, N):
+        raise KernelError(f"wkv_decay: low {tuple(low.shape)}, w2 {tuple(w2.shape)}, out {tuple(out.shape)}")
+    _call("mllm_wkv_decay", low.data_ptr(), _rows("low", low), w2.data_ptr(), w0.data_ptr(), out.data_ptr(), _rows("out", out),
+          T, N, R, _dt(low), _stream())
+
+
+def wkv_scan(r, k, v, w, u, h, state, prev_off: int, ctx, out, *, heads: int, write_state: bool = True) -> None:
+    """The recurrence of csrc/wkv.cu over the step's tokens, request by request: o = (S + diag(u) k v^T)^T r;
+    S <- diag(w) S + k v^T.  r, k, v [T, heads * n] in one dtype; w (the decays, ``wkv_decay``) float32 [T, heads * n];
+    u float32 [heads * n]; state float32 [slots, row] with S [heads, n, n] at column 0 and the last row of h
     [T, D] of every request kept at column ``prev_off``; out float32 [T, heads * n]."""
     _cuda("r", r, contiguous=False)
-    for name, t in (("k", k), ("v", v), ("low", low), ("h", h)):
+    for name, t in (("k", k), ("v", v), ("h", h)):
         _cuda(name, t, r.dtype, contiguous=False)
-    _cuda("w2", w2, r.dtype)
-    _cuda("w0", w0, torch.float32)
+    _cuda("w", w, torch.float32, contiguous=False)
     _cuda("u", u, torch.float32)
     _cuda("state", state, torch.float32)
     _cuda("out", out, torch.float32, contiguous=False)
     T = r.shape[0]
     n = r.shape[1] // heads
-    R = low.shape[1]
     D = h.shape[1]
     if n > WKV_MAX_DIM or r.shape[1] != heads * n or tuple(k.shape) != tuple(r.shape) or tuple(v.shape) != tuple(r.shape) \
-            or tuple(out.shape) != tuple(r.shape) or tuple(w2.shape) != (heads * n, R) or w0.numel() != heads * n \
-            or u.numel() != heads * n or low.shape[0] != T or h.shape[0] != T or state.dim() != 2 \
-            or state.shape[1] < max(heads * n * n, prev_off + D) or prev_off < heads * n * n:
+            or tuple(out.shape) != tuple(r.shape) or tuple(w.shape) != tuple(r.shape) or u.numel() != heads * n \
+            or h.shape[0] != T or state.dim() != 2 or state.shape[1] < max(heads * n * n, prev_off + D) \
+            or prev_off < heads * n * n:
         raise KernelError("wkv_scan: shapes do not fit")
     _call("mllm_wkv_scan", r.data_ptr(), _rows("r", r), k.data_ptr(), _rows("k", k), v.data_ptr(), _rows("v", v),
-          low.data_ptr(), _rows("low", low), w2.data_ptr(), w0.data_ptr(), u.data_ptr(), h.data_ptr(), _rows("h", h),
-          state.data_ptr(), state.stride(0), int(prev_off), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(),
-          _rows("out", out), ctx.S, int(heads), n, R, D, int(write_state), _dt(r), _stream())
+          w.data_ptr(), _rows("w", w), u.data_ptr(), h.data_ptr(), _rows("h", h), state.data_ptr(), state.stride(0),
+          int(prev_off), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), _rows("out", out), ctx.S,
+          int(heads), n, D, int(write_state), _dt(r), _stream())
 
 
 def wkv_finish(o, z, weight, out, *, heads: int, eps: float) -> None:

@@ -254,7 +254,9 @@ def test_recurrence_in_unequal_portions_and_batches(ops, dtype, Hr, n, R, D):
         t = {k: (v[rows] if v.shape[0] == sum(lens) and k not in ("w2",) else v) for k, v in full.items()}
         _, ctx = _wkv_case([step[i] for i in live], Hr, n, R, D, dtype, seed=0, slots=[slots[i] for i in live])
         out = torch.empty(rows.numel(), N, device=DEV)
-        ops.wkv_scan(t["r"], t["k"], t["v"], t["low"], full["w2"], full["w0"], full["u"], t["h"], state, N * n, ctx, out, heads=Hr)
+        dec = torch.empty(rows.numel(), N, device=DEV)
+        ops.wkv_decay(t["low"], full["w2"], full["w0"], dec)
+        ops.wkv_scan(t["r"], t["k"], t["v"], dec, full["u"], t["h"], state, N * n, ctx, out, heads=Hr)
         ops.check_device_errors()
         o = 0
         for i in live:
@@ -274,8 +276,10 @@ def test_recurrence_in_unequal_portions_and_batches(ops, dtype, Hr, n, R, D):
         assert torch.equal(state[slots[i], N * n:].cpu(), full["h"][starts[i] + L - 1].float().cpu())
         _, ctx = _wkv_case([L], Hr, n, R, D, dtype, seed=0, slots=[slots[i]])
         out = torch.empty(L, N, device=DEV)
-        ops.wkv_scan(full["r"][sl], full["k"][sl], full["v"][sl], full["low"][sl], full["w2"], full["w0"], full["u"], full["h"][sl],
-                     one, N * n, ctx, out, heads=Hr)
+        dec_all = torch.empty(L, N, device=DEV)
+        ops.wkv_decay(full["low"][sl], full["w2"], full["w0"], dec_all)
+        assert (dec_all.double().cpu() - dec).abs().max() < 3e-6         # the decays themselves, in (0, 1)
+        ops.wkv_scan(full["r"][sl], full["k"][sl], full["v"][sl], dec_all, full["u"], full["h"][sl], one, N * n, ctx, out, heads=Hr)
         assert torch.equal(one[slots[i]], state[slots[i]])       # the same bits however the tokens were cut
     assert torch.all(state[1] == 9.0)
     # the channel that never forgets still holds the first token's k v^T; the one that forgets at once only the last token's
