@@ -48,15 +48,27 @@ wkv_shift_kernel(const T* h, long long ldh, const float* __restrict__ mu, const 
 }
 
 // w[t][c] = exp(-exp(w0[c] + sum_q W2[c][q] tanh(low[t][q]))): a CTA takes 16 tokens and 64 channels; the tokens' tanh
-// values are staged in shared memory, a thread keeps one channel's sums for four tokens.  Every token's sum runs over q in
-// the same order, whatever else is in the step.
-constexpr int DEC_TOK = 16, DEC_CH = 64;
+// values and (64 ranks at a time) the channels' rows of W2 are staged in shared memory with loads along the rows, a
+// thread keeps one channel's sums for four tokens.  Every token's sum runs over q in the same order, whatever else is
+// in the step.
+constexpr int DEC_TOK = 16, DEC_CH = 64, DEC_Q = 64;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 wkv_decay_kernel(const T* low, long long l_stride, const T* __restrict__ W2, const float* __restrict__ w0, float* __restrict__ w,
                  long long w_stride, int Tn, int N, int R) {
-    extern __shared__ float tl[];           // [DEC_TOK][R]
+    extern __shared__ float tl[];           // [DEC_TOK][R], then the tile of W2 [DEC_Q][DEC_CH + 1]
+    float* wt = tl + DEC_TOK * R;
+    const int ch0 = blockIdx.y * DEC_CH;
+    const int chl = threadIdx.x & (DEC_CH - 1), tg = threadIdx.x / DEC_CH;     // this thread's channel; tokens tg, tg + 4, ...
+    const int ch = ch0 + chl;
+    auto stage_w = [&](int q0) {            // weights: may be read before the kernel before this one has ended
+        for (int idx = threadIdx.x; idx < DEC_CH * DEC_Q; idx += blockDim.x) {
+            const int c = idx / DEC_Q, q = idx % DEC_Q;
+            wt[q * (DEC_CH + 1) + c] = (ch0 + c < N && q0 + q < R) ? to_f32(W2[(size_t)(ch0 + c) * R + q0 + q]) : 0.f;
+        }
+    };
+    stage_w(0);
     pdl_wait();
     pdl_launch();
     const int t0 = blockIdx.x * DEC_TOK, nt = min(DEC_TOK, Tn - t0);
@@ -64,20 +76,24 @@ wkv_decay_kernel(const T* low, long long l_stride, const T* __restrict__ W2, con
         const int c = idx / R, q = idx % R;
         tl[idx] = c < nt ? tanhf(to_f32(low[(size_t)(t0 + c) * l_stride + q])) : 0.f;
     }
-    __syncthreads();
-    const int ch = blockIdx.y * DEC_CH + (threadIdx.x & (DEC_CH - 1)), tg = threadIdx.x / DEC_CH;     // tokens tg, tg + 4, ...
-    if (ch >= N) return;
-    const float b = w0[ch];
     float acc[DEC_TOK / 4];
+    const float b = ch < N ? w0[ch] : 0.f;
 #pragma unroll
     for (int u = 0; u < DEC_TOK / 4; ++u) acc[u] = b;
-    const T* wr = W2 + (size_t)ch * R;
-#pragma unroll 8
-    for (int q = 0; q < R; ++q) {
-        const float wv = to_f32(wr[q]);
+    for (int q0 = 0; q0 < R; q0 += DEC_Q) {
+        if (q0 > 0) {
+            __syncthreads();                // the tile before is no longer read
+            stage_w(q0);
+        }
+        __syncthreads();
+        const int nq = min(DEC_Q, R - q0);
+        for (int q = 0; q < nq; ++q) {
+            const float wv = wt[q * (DEC_CH + 1) + chl];
 #pragma unroll
-        for (int u = 0; u < DEC_TOK / 4; ++u) acc[u] = fmaf(wv, tl[(tg + 4 * u) * R + q], acc[u]);
+            for (int u = 0; u < DEC_TOK / 4; ++u) acc[u] = fmaf(wv, tl[(tg + 4 * u) * R + q0 + q], acc[u]);
+        }
     }
+    if (ch >= N) return;
 #pragma unroll
     for (int u = 0; u < DEC_TOK / 4; ++u) {
         const int c = tg + 4 * u;
@@ -270,7 +286,7 @@ MLLM_EXPORT int mllm_wkv_decay(const void* low, long long l_stride, const void* 
                                int T, int N, int R, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (N <= 0 || R <= 0) return mllm_fail(1, "wkv_decay: %d channels, rank %d", N, R);
-    const size_t smem = sizeof(float) * (size_t)DEC_TOK * R;
+    const size_t smem = sizeof(float) * ((size_t)DEC_TOK * R + DEC_Q * (DEC_CH + 1));
     if (smem > 96 * 1024) return mllm_fail(1, "wkv_decay: rank %d does not fit shared memory", R);
     const dim3 grid((T + DEC_TOK - 1) / DEC_TOK, (N + DEC_CH - 1) / DEC_CH);
     if (grid.y > 65535) return mllm_fail(1, "wkv_decay: too many channels");

@@ -49,7 +49,7 @@ class WKVMixer(Mixer):
         out = []
         if self.head_dim > ops.WKV_MAX_DIM:
             out.append(f"wkv: heads of {self.head_dim} entries; the kernel takes {ops.WKV_MAX_DIM}")
-        if self.decay_rank is not None and self.decay_rank * 64 > 96 * 1024:
+        if self.decay_rank is not None and self.decay_rank * 64 + 17 * 1024 > 96 * 1024:
             out.append(f"wkv: a decay of rank {self.decay_rank} does not fit the shared memory of the recurrence kernel")
         return out
 
@@ -63,9 +63,9 @@ class WKVMixer(Mixer):
             self.mu = torch.stack([params[f"mu_{s}"] for s in MIXES]).contiguous()
             self.u_flat = self.u.reshape(-1).contiguous()
             self.rank = int(self.w1_weight.shape[0])
-            if self.w2_weight.shape[1] != self.rank or self.rank * 64 > 96 * 1024:
+            if self.w2_weight.shape[1] != self.rank or self.rank * 64 + 17 * 1024 > 96 * 1024:
                 raise ValueError(f"wkv: the decay's matrices have ranks {self.rank} and {self.w2_weight.shape[1]} "
-                                 f"(equal, and at most {96 * 1024 // 64})")
+                                 f"(equal, and at most {(96 - 17) * 1024 // 64})")
 
     def forward(self, h, ctx, cache, out_accum, accumulate: bool = True):
         import torch

@@ -354,6 +354,30 @@ def test_sizes_that_happen_to_be_one_or_equal(tmp_path):
         assert np.isfinite(out).all()
 
 
+def test_odd_sizes(tmp_path):
+    """A width, head sizes, value sizes, inner sizes and a vocabulary that are no multiples of 8 (rows that start on no
+    16-byte boundary), a recurrence of 33 entries per head with a decay of rank 70 (two tiles of its weights), three query
+    heads per key/value head: every product and kernel takes them, in both dtypes."""
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+    cfg = config(50, 77, 1e-5, 1.5, [layer(wkv(2, 33, 70), moe(5, 2, 10, 1.2)),
+                                     layer(attn(3, 1, 6, 5, 0.9, (4, 50.0), v_mix=True), dense(30)),
+                                     layer(attn2(3, 1, 10, 5, 0.8, 9, 4.0, v_mix=True), moe(6, 2, 7, 0.9, groups=(3, 1))),
+                                     layer(wkv(3, 5, 1), dense(13))])
+    tensors = make_tensors(cfg, 6)
+    folder = write_model(str(tmp_path / "odd"), clean(cfg), tensors, torch.bfloat16)
+    ids = random_ids(150, cfg["vocab"], 3)
+    for dtype in ("float32", "bfloat16"):
+        want = oracle(tensors, cfg, ids, dtype)
+        r = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=8, num_pages=40, max_num_seqs=2, use_cuda_graphs=False))
+        r.add_request("a")
+        rows = [r.step([StepEntry("a", ids[:97], list(range(97)))]).cpu().numpy()]
+        rows.append(r.step([StepEntry("a", ids[97:120], list(range(23)))]).cpu().numpy())
+        for t in range(120, 150):
+            rows.append(r.step([StepEntry("a", [ids[t]], [0])]).cpu().numpy())
+        close(np.concatenate(rows), want, dtype, "odd sizes")
+
+
 def test_command_line_with_random_weights(tmp_path):
     """bin/mini_llm: the random-weights mode writes a Kusirax folder from a config.json (the decay's rank given there);
     greedy tokens from the command line equal LLM.generate's."""
