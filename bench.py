@@ -483,7 +483,7 @@ def design_configs(size: str):
                    logit_softcap=30.0)
     # Kusirax at the same width, heads and key/value heads: recurrent layers (heads of 64 entries over the whole width, a
     # decay of rank 64) around a rotary attention layer (half of every head turns, frequencies scaled by wavelength) and an
-    # attention_2 layer (biases, scores capped at 50, slopes, blocks of 768 positions), all attention layers mixing their
+    # attention_2 layer (biases, scores capped at 30, slopes, blocks of 768 positions), all attention layers mixing their
     # values; dense feed-forwards of Finuvik's inner size alternate with 8 experts without gates in 4 groups of which 2
     # are kept, two per token, of 3/8 of it (two matrices instead of three: as many weights per token as Mumopel's)
     kinds = ["wkv", "attention", "attention_2", "wkv"]
@@ -495,11 +495,11 @@ def design_configs(size: str):
         else:
             mixer = dict(heads=H, kv_heads=z["kv_heads"], dim=dh, vdim=dh, scale=dh ** -0.5, v_mix=True)
             if kind == "attention":
-                mixer["rot"] = dict(base=10000.0, dims=dh // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=512))
+                mixer["rot"] = dict(base=10000.0, dims=dh // 2, scaling=dict(factor=4.0, low=1.0, high=8.0, original=512))
             else:
-                mixer.update(mask=dict(size=768), softcap=50.0)
+                mixer.update(mask=dict(size=768), softcap=30.0)
         mlp = dict(kind="dense", ff=F) if i % 2 == 0 else \
-            dict(kind="moe", router=dict(experts=8, top=2, scale=2.5, groups=dict(count=4, keep=2)), expert=dict(ff=3 * F // 8 // 8 * 8))
+            dict(kind="moe", router=dict(experts=8, top=2, scale=2.0, groups=dict(count=4, keep=2)), expert=dict(ff=3 * F // 8 // 8 * 8))
         kl.append(dict(type=kind, mixer=mixer, mlp=mlp))
     kusirax = dict(architecture="Kusirax", width=D, vocab=DESIGN_VOCAB, norm=dict(eps=1e-5), postln_alpha=2.0, layers=kl)
     return {"gpt2": gpt2, "finuvik": finuvik, "falisun": falisun, "mumopel": mumopel, "kusirax": kusirax}

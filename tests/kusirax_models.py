@@ -76,12 +76,12 @@ CFG_A = config(64, 97, 1e-5, 2.0, [
     layer(wkv(1, 40, 3), moe(4, 1, 16, 1.0)),
 ])
 # B: starts with a recurrence of two heads of 64 (rank 16).  A rotary attention of sizes the tensor-core kernel takes (32 /
-# 32) whose heads turn whole, without scaling and without value mixing, eight experts in two groups of which one is kept.
+# 32) whose heads turn whole, without scaling and without value mixing, ten experts in two groups of which one is kept.
 # An attention_2 of eight heads over two with values three times as wide as keys, blocks of 100, no cap, the only
 # value-mixing layer.  An attention_2 of one head of 64, blocks of 7, a tight cap.  A recurrence of five heads of 8.
 CFG_B = config(96, 211, 1e-6, 3.5, [
     layer(wkv(2, 64, 16), dense(40)),
-    layer(attn(4, 4, 32, 32, 0.4, (32, 10000.0)), moe(8, 3, 16, 2.5, groups=(2, 1))),
+    layer(attn(4, 4, 32, 32, 0.4, (32, 10000.0)), moe(10, 4, 16, 1.9, groups=(2, 1))),
     layer(attn2(8, 2, 16, 48, 0.8, 100, None, v_mix=True), dense(56)),
     layer(attn2(1, 1, 64, 16, 0.5, 7, 2.0), moe(3, 3, 8, 0.8)),
     layer(wkv(5, 8, 2), None),

@@ -302,7 +302,7 @@ def test_long_contexts_with_a_key_far_back(tmp_path):
     from mini_llm_b200.config.base import EngineConfig
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
     cfg = config(72, 131, 1e-5, 2.0, [
-        layer(attn(4, 2, 16, 16, 0.8, (8, 10000.0), scaling=(8.0, 1.0, 4.0, 256), v_mix=True), dense(48)),
+        layer(attn(4, 2, 16, 16, 0.8, (8, 10000.0), scaling=(6.0, 1.0, 4.0, 256), v_mix=True), dense(48)),
         layer(attn2(3, 1, 24, 32, 0.7, 700, 10.0, v_mix=True), moe(4, 2, 16, 1.5, groups=(2, 2))),
         layer(wkv(2, 32, 6), None),
         layer(attn2(2, 2, 32, 16, 0.6, 1024, None, v_mix=True), None)])

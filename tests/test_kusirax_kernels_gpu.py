@@ -37,7 +37,7 @@ def _tol(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dk,dv,rot,base,scaling", [
     (6, 2, 20, 12, 8, 100.0, (4.0, 1.0, 4.0, 32)), (2, 2, 16, 16, 16, 20.0, None), (4, 1, 8, 24, 0, 10.0, None),
-    (3, 3, 32, 32, 16, 3e4, (8.0, 0.5, 2.0, 100)), (1, 1, 64, 16, 64, 1e6, (8.0, 1.0, 4.0, 512)), (5, 5, 6, 2, 2, 3.0, None),
+    (3, 3, 32, 32, 16, 3e4, (8.0, 0.5, 2.0, 100)), (1, 1, 64, 16, 64, 2e5, (6.0, 1.0, 4.0, 512)), (5, 5, 6, 2, 2, 3.0, None),
     (8, 2, 128, 128, 64, 1e4, (2.0, 1.0, 8.0, 64))])
 def test_rotation_unit_norm_per_head_and_value_mixing(ops, dtype, H, G, dk, dv, rot, base, scaling):
     from mini_llm_b200.parts.rotary import rotary_table
@@ -124,8 +124,8 @@ def _run(ops, case, impl, chunk=None, cap=None, slopes=False):
 
 
 SHAPES = [(4, 2, 16, 24, 8), (3, 3, 32, 32, 16), (6, 1, 96, 40, 4), (2, 2, 8, 1, 16), (4, 2, 20, 12, 8), (8, 2, 48, 32, 16)]
-VARIANTS = [dict(chunk=24, cap=3.0, slopes=True), dict(chunk=37, slopes=True), dict(cap=1.5), dict(chunk=64, cap=50.0, slopes=True),
-            dict(chunk=7, cap=2.0, slopes=True), dict(slopes=True), dict(chunk=120, cap=8.0, slopes=True)]
+VARIANTS = [dict(chunk=24, cap=3.0, slopes=True), dict(chunk=37, slopes=True), dict(cap=1.5), dict(chunk=64, cap=45.0, slopes=True),
+            dict(chunk=7, cap=2.0, slopes=True), dict(slopes=True), dict(chunk=112, cap=8.0, slopes=True)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -169,7 +169,7 @@ def test_capped_scores_and_slopes_for_single_tokens(ops, dtype, H, G, dk, dv, pa
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("impl", ["simt", "tiled", "split", "mma"])
-@pytest.mark.parametrize("chunk", [48, 120, 64])
+@pytest.mark.parametrize("chunk", [48, 112, 64])
 def test_keys_just_inside_and_just_outside_a_block_under_a_cap(ops, impl, dtype, chunk):
     """Sharp keys on both sides of every block's first position, at page (16), key-tile (32, 64) and split edges and at
     the first positions; the cap (40) leaves their scores standing out and the slopes pull on the far ones.  A query sees
@@ -331,7 +331,7 @@ def test_unit_norm_weight_and_gate(ops, dtype, T, Hr, n):
 
 # ------------------------------------------------------------------------------------------------ the norm after the sum
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16, None])
-@pytest.mark.parametrize("T,D,top,alpha", [(1, 64, 0, 3.0), (37, 320, 3, 2.0), (5, 1536, 2, 0.5), (130, 40, 1, 1.0)])
+@pytest.mark.parametrize("T,D,top,alpha", [(1, 64, 0, 1.5), (37, 352, 3, 2.0), (5, 1536, 2, 0.5), (130, 40, 1, 1.0)])
 def test_norm_after_the_sum(ops, out_dtype, T, D, top, alpha):
     eps = 1e-6
     x0 = rnd(T, D, seed=1, scale=2.0)
@@ -355,7 +355,7 @@ def test_norm_after_the_sum(ops, out_dtype, T, D, top, alpha):
 # ------------------------------------------------------------------------------------------------ router and experts
 @pytest.mark.parametrize("T", [1, 7, 16, 17, 300])
 @pytest.mark.parametrize("E,top,groups,keep,D", [(6, 3, 3, 2, 64), (16, 4, 4, 2, 192), (4, 1, 1, 1, 96), (3, 3, 1, 1, 40),
-                                                 (8, 3, 2, 1, 320), (64, 8, 8, 4, 128), (4, 2, 4, 2, 32), (1, 1, 1, 1, 8)])
+                                                 (10, 3, 2, 1, 272), (64, 8, 8, 4, 128), (4, 2, 4, 2, 32), (1, 1, 1, 1, 8)])
 def test_router_over_sigmoid_scores_and_group_sums(ops, T, E, top, groups, keep, D):
     for dtype in (torch.float32, torch.bfloat16):
         h = rnd(T, D, seed=T + E, dtype=dtype)
@@ -365,8 +365,8 @@ def test_router_over_sigmoid_scores_and_group_sums(ops, T, E, top, groups, keep,
         offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
         order = torch.empty(T * top, dtype=torch.int32, device=DEV)
         ops.moe_route(h, router, idx, wts, offsets, order, top=top, groups=groups, keep=keep, mode="sigmoid", group_sum=2,
-                      weight_scale=2.5)
-        r = dict(top=top, scale=2.5, groups=dict(count=groups, keep=keep))
+                      weight_scale=1.9)
+        r = dict(top=top, scale=1.9, groups=dict(count=groups, keep=keep))
         wi, ww = P.route(h.double().cpu(), router.double().cpu(), r)
         gi, gw = idx.long().cpu(), wts.double().cpu()
         flips = 0
@@ -375,7 +375,7 @@ def test_router_over_sigmoid_scores_and_group_sums(ops, T, E, top, groups, keep,
                 flips += 1
                 continue
             assert (gw[t] - ww[t]).abs().max() < 2e-5
-            assert abs(float(gw[t].sum()) - 2.5) < 1e-5
+            assert abs(float(gw[t].sum()) - 1.9) < 1e-5
         assert flips <= max(1, T // 50)
         off, od = offsets.cpu().tolist(), order.cpu().tolist()
         assert off[0] == 0 and off[-1] == T * top and sorted(od) == list(range(T * top))
@@ -409,7 +409,7 @@ def test_a_group_is_scored_by_its_two_largest_and_scores_are_not_a_softmax(ops):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,E,top,D,F", [(1, 5, 2, 64, 24), (9, 12, 3, 192, 48), (40, 4, 1, 96, 16), (200, 3, 3, 96, 8),
-                                         (70, 8, 2, 768, 512), (16, 8, 2, 128, 40), (33, 6, 3, 320, 96)])
+                                         (70, 8, 2, 768, 512), (16, 8, 2, 128, 40), (33, 6, 3, 288, 80)])
 def test_experts_without_gates(ops, dtype, T, E, top, D, F):
     """Route, the experts' two products with the square of relu between them, the weighted sum: against the statement
     with the router's own choice (so that a near-tie upstream does not decide the comparison)."""
