@@ -10,7 +10,8 @@
 // to S, so that the next step finds it.  State, decay (tanh, both exponentials), the update, o, the norm and the gate
 // are 32-bit whatever the dtype of the projections.
 //
-// Four kernels.  `shift`: the mixes of every token (one CTA per token).  `decay`: the decays of every token and channel,
+// Five kernels.  `step`: steps of single tokens in one launch (decay, update, output, norm and gate; described where it
+// stands).  The other four take steps that carry prompt portions.  `shift`: the mixes of every token (one CTA per token).  `decay`: the decays of every token and channel,
 // off the recurrence's sequential path.  `scan`: a CTA takes 32 columns of one
 // (request, head)'s state; thread (lane, g) keeps rows g*WR .. g*WR+WR-1 of column lane in registers for the whole walk,
 // tokens come CH at a time (r, k, the decays and v staged in shared memory, the next chunk's fetched into registers
@@ -259,6 +260,99 @@ wkv_finish_kernel(const float* o, long long o_stride, const T* z, long long z_st
     }
 }
 
+// Steps of single tokens: the decay, the state's update, the output, its unit norm, the weight and the gate in one
+// launch.  One CTA per (request, head); thread (column j, row group g) keeps RK rows of column j of the state in
+// registers.  The head's rows of W2 come into shared memory with loads along the rows before the kernel waits for its
+// predecessor (they are weights).  The decays are the same bits as the decay pass's (one sum per channel over q in
+// order), and every state element takes the same update as in the scan, so the state is the same bits whichever kernel
+// took a token.  A request's tokens (one in a decode step) are walked in order.
+template <typename T, int RK>
+__global__ void __launch_bounds__(1024)
+wkv_step_kernel(const T* r, const T* k, const T* v, const T* low, const T* __restrict__ W2, const float* __restrict__ w0,
+                const T* z, const float* __restrict__ weight, const T* h, T* __restrict__ y, long long l_stride,
+                long long z_stride, long long y_stride, int R, int evp, float eps, WkvArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float scratch[33];
+    const int n = a.n, tid = threadIdx.x, nthreads = blockDim.x;
+    const int G = nthreads / evp, j = tid % evp, g = tid / evp;
+    float* w2s = sm;                          // [n][R + 1]
+    float* tl = w2s + n * (R + 1);            // [R]
+    float* rs = tl + R;                       // [n]
+    float* ks = rs + n;                       // [n]
+    float* ws = ks + n;                       // [n]
+    float* vs = ws + n;                       // [evp]
+    float* os = vs + evp;                     // [G][evp]
+    const int seq = blockIdx.x, hd = blockIdx.y;
+    for (int idx = tid; idx < n * R; idx += nthreads) {
+        const int i = idx / R, q = idx % R;
+        w2s[i * (R + 1) + q] = to_f32(W2[((size_t)hd * n + i) * R + q]);
+    }
+    pdl_wait();
+    pdl_launch();
+    const int t0 = a.cu_q[seq], t1 = a.cu_q[seq + 1];
+    if (t1 <= t0) return;
+    const int slot = a.slots[seq];
+    const bool col = j < n;
+    float* sp = a.state + (size_t)slot * a.state_stride + ((size_t)hd * n) * n + j;
+    float s[RK], uu[RK];
+#pragma unroll
+    for (int i = 0; i < RK; ++i) {
+        const int row = g * RK + i;
+        s[i] = (col && row < n) ? sp[(size_t)row * n] : 0.f;
+        uu[i] = row < n ? a.u[hd * n + row] : 0.f;
+    }
+    if (a.write_state && hd == 0) {
+        float* kept = a.state + (size_t)slot * a.state_stride + a.prev_off;
+        const T* last = h + (size_t)(t1 - 1) * a.h_stride;
+        for (int d = tid; d < a.D; d += nthreads) kept[d] = to_f32(last[d]);
+    }
+    for (int t = t0; t < t1; ++t) {
+        __syncthreads();                      // the token before is no longer read; the weights are staged
+        for (int q = tid; q < R; q += nthreads) tl[q] = tanhf(to_f32(low[(size_t)t * l_stride + q]));
+        for (int i = tid; i < n; i += nthreads) {
+            rs[i] = to_f32(r[(size_t)t * a.r_stride + (size_t)hd * n + i]);
+            ks[i] = to_f32(k[(size_t)t * a.k_stride + (size_t)hd * n + i]);
+        }
+        for (int d = tid; d < evp; d += nthreads) vs[d] = d < n ? to_f32(v[(size_t)t * a.v_stride + (size_t)hd * n + d]) : 0.f;
+        __syncthreads();
+        for (int i = tid; i < n; i += nthreads) {
+            float acc = w0[hd * n + i];
+            const float* wr = w2s + i * (R + 1);
+            for (int q = 0; q < R; ++q) acc = fmaf(wr[q], tl[q], acc);
+            ws[i] = expf(-expf(acc));
+        }
+        __syncthreads();
+        const float vj = vs[j];
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < RK; ++i) {
+            const int row = g * RK + i;
+            if (row < n) {
+                const float kv = ks[row] * vj;
+                acc = fmaf(rs[row], fmaf(uu[i], kv, s[i]), acc);
+                s[i] = fmaf(ws[row], s[i], kv);
+            }
+        }
+        os[g * evp + j] = acc;
+        __syncthreads();
+        float o = 0.f;
+        if (g == 0 && col) {                  // the row groups meet in group order
+            o = os[j];
+            for (int gg = 1; gg < G; ++gg) o += os[gg * evp + j];
+        }
+        const float inv = 1.0f / sqrtf(block_sum(o * o, scratch) / (float)n + eps);
+        if (g == 0 && col) {
+            const float zz = to_f32(z[(size_t)t * z_stride + (size_t)hd * n + j]);
+            y[(size_t)t * y_stride + (size_t)hd * n + j] = from_f32<T>(o * inv * weight[hd * n + j] * (zz / (1.0f + expf(-zz))));
+        }
+    }
+    if (a.write_state && col) {
+#pragma unroll
+        for (int i = 0; i < RK; ++i)
+            if (g * RK + i < n) sp[(size_t)(g * RK + i) * n] = s[i];
+    }
+}
+
 }  // namespace
 
 MLLM_EXPORT int mllm_wkv_max_dim() { return 256; }
@@ -352,5 +446,47 @@ MLLM_EXPORT int mllm_wkv_finish(const float* o, long long o_stride, const void* 
                               (const __nv_bfloat16*)z, z_stride, weight, (__nv_bfloat16*)y, y_stride, T, Hr, n, eps));
     else
         return mllm_fail(1, "wkv_finish: unknown dtype code %d", dtype);
+    return 0;
+}
+
+// 1 when the single-launch kernel for steps of single tokens takes heads of n entries with a decay of rank R
+MLLM_EXPORT int mllm_wkv_step_ok(int n, int R) {
+    if (n <= 0 || n > 128 || R <= 0) return 0;
+    const int evp = (n + 31) / 32 * 32, G = 1024 / evp;
+    const size_t smem = sizeof(float) * ((size_t)n * (R + 1) + R + 3 * (size_t)n + evp + (size_t)G * evp);
+    return smem <= 160 * 1024 ? 1 : 0;
+}
+
+// The recurrence of a step of single tokens in one launch: decays from low [T, R], W2 and w0, the update of the state,
+// o, and y = o / sqrt(mean(o^2) + eps) * weight * silu(z) per head, [T, Hr*n] in `dtype`.
+MLLM_EXPORT int mllm_wkv_step(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
+                              long long v_stride, const void* low, long long l_stride, const void* W2, const float* w0,
+                              const float* u, const void* z, long long z_stride, const float* weight, const void* h,
+                              long long h_stride, float* state, long long state_stride, long long prev_off, const int* cu_q,
+                              const int* slots, void* y, long long y_stride, int S, int Hr, int n, int R, int D, float eps,
+                              int write_state, int dtype, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    if (!mllm_wkv_step_ok(n, R) || Hr <= 0 || Hr > 65535) return mllm_fail(1, "wkv_step: %d heads of %d, rank %d", Hr, n, R);
+    const int evp = (n + 31) / 32 * 32, G = 1024 / evp;
+    const int rk = (n + G - 1) / G;
+    const size_t smem = sizeof(float) * ((size_t)n * (R + 1) + R + 3 * (size_t)n + evp + (size_t)G * evp);
+    WkvArgs a{cu_q, slots, u, state, state_stride, prev_off, r_stride, k_stride, v_stride, 0, 0, h_stride, Hr, n, D, write_state};
+    const dim3 grid(S, Hr), block(evp * G);
+#define MLLM_STEP(TT, RKK)                                                                                               \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024)                                                                                            \
+            MLLM_CUDA(cudaFuncSetAttribute(wkv_step_kernel<TT, RKK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MLLM_CUDA(mllm_launch(wkv_step_kernel<TT, RKK>, grid, block, smem, stream, true, (const TT*)r, (const TT*)k,    \
+                              (const TT*)v, (const TT*)low, (const TT*)W2, w0, (const TT*)z, weight, (const TT*)h, (TT*)y, \
+                              l_stride, z_stride, y_stride, R, evp, eps, a));                                            \
+    } while (0)
+    if (dtype == MLLM_F32) {
+        if (rk <= 4) MLLM_STEP(float, 4); else MLLM_STEP(float, 16);
+    } else if (dtype == MLLM_BF16) {
+        if (rk <= 4) MLLM_STEP(__nv_bfloat16, 4); else MLLM_STEP(__nv_bfloat16, 16);
+    } else {
+        return mllm_fail(1, "wkv_step: unknown dtype code %d", dtype);
+    }
+#undef MLLM_STEP
     return 0;
 }

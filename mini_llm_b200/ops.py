@@ -107,6 +107,10 @@ def _signatures(lib):
                            c_int, c_float, c_int, c_void_p],
         "mllm_wkv_shift": [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_wkv_step_ok": [c_int, c_int],
+        "mllm_wkv_step": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
+                          c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_wkv_decay": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_wkv_scan": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p,
                           c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -1165,6 +1169,40 @@ def wkv_scan(r, k, v, w, u, h, state, prev_off: int, ctx, out, *, heads: int, wr
           w.data_ptr(), _rows("w", w), u.data_ptr(), h.data_ptr(), _rows("h", h), state.data_ptr(), state.stride(0),
           int(prev_off), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), _rows("out", out), ctx.S,
           int(heads), n, D, int(write_state), _dt(r), _stream())
+
+
+def wkv_step_ok(n: int, rank: int) -> bool:
+    """Whether the single-launch kernel for steps of single tokens takes heads of ``n`` entries with a decay of this rank."""
+    return bool(library().mllm_wkv_step_ok(int(n), int(rank)))
+
+
+def wkv_step(r, k, v, low, w2, w0, u, z, weight, h, state, prev_off: int, ctx, out, *, heads: int, eps: float,
+             write_state: bool = True) -> None:
+    """A step of single tokens of csrc/wkv.cu's recurrence in one launch: what ``wkv_decay``, ``wkv_scan`` and
+    ``wkv_finish`` do one after the other (the same decays and the same state bit for bit; the outputs' sums over the
+    state's rows meet in another grouping).  r, k, v, z, out [T, heads * n], low [T, R], w2 [heads * n, R], h [T, D] in one
+    dtype; w0, u, weight float32 [heads * n]; state as for ``wkv_scan``."""
+    _cuda("r", r, contiguous=False)
+    for name, t in (("k", k), ("v", v), ("low", low), ("z", z), ("h", h), ("out", out)):
+        _cuda(name, t, r.dtype, contiguous=False)
+    _cuda("w2", w2, r.dtype)
+    for name, t in (("w0", w0), ("u", u), ("weight", weight), ("state", state)):
+        _cuda(name, t, torch.float32)
+    T = r.shape[0]
+    n = r.shape[1] // heads
+    R = low.shape[1]
+    D = h.shape[1]
+    if r.shape[1] != heads * n or any(tuple(t.shape) != tuple(r.shape) for t in (k, v, z, out)) or tuple(w2.shape) != (heads * n, R) \
+            or w0.numel() != heads * n or u.numel() != heads * n or weight.numel() != heads * n or low.shape[0] != T \
+            or h.shape[0] != T or state.dim() != 2 or state.shape[1] < max(heads * n * n, prev_off + D) or prev_off < heads * n * n:
+        raise KernelError("wkv_step: shapes do not fit")
+    if not wkv_step_ok(n, R):
+        raise KernelError(f"wkv_step: heads of {n} entries with rank {R} go through wkv_decay, wkv_scan and wkv_finish")
+    _call("mllm_wkv_step", r.data_ptr(), _rows("r", r), k.data_ptr(), _rows("k", k), v.data_ptr(), _rows("v", v), low.data_ptr(),
+          _rows("low", low), w2.data_ptr(), w0.data_ptr(), u.data_ptr(), z.data_ptr(), _rows("z", z), weight.data_ptr(),
+          h.data_ptr(), _rows("h", h), state.data_ptr(), state.stride(0), int(prev_off), ctx.cu_q.data_ptr(),
+          ctx.state_slots.data_ptr(), out.data_ptr(), _rows("out", out), ctx.S, int(heads), n, R, D, float(eps),
+          int(write_state), _dt(r), _stream())
 
 
 def wkv_finish(o, z, weight, out, *, heads: int, eps: float) -> None:

@@ -86,12 +86,18 @@ class WKVMixer(Mixer):
         ops.linear(mixes[2], self.v_weight, None, out=v)
         ops.linear(mixes[3], self.g_weight, None, out=g)
         ops.linear(mixes[4], self.w1_weight, None, out=low)
+        mid = ctx.ws.buf("mix_core", T, N, act)
+        if getattr(ctx, "decode_only", False) and ops.wkv_step_ok(self.head_dim, self.rank):
+            # single tokens: decay, update, output, norm and gate in one launch
+            ops.wkv_step(r, k, v, low, self.w2_weight, self.w0, self.u_flat, g, self.norm_weight, h, cache.state, self.s_floats,
+                         ctx, mid, heads=self.num_heads, eps=self.norm_eps, write_state=cache.write)
+            ops.linear(mid, self.out_weight, None, out=out_accum, accumulate=accumulate)
+            return
         dec = ctx.ws.buf("wkv_decay", T, N, torch.float32)
         ops.wkv_decay(low, self.w2_weight, self.w0, dec)
         raw = ctx.ws.buf("wkv_raw", T, N, torch.float32)
         ops.wkv_scan(r, k, v, dec, self.u_flat, h, cache.state, self.s_floats, ctx, raw, heads=self.num_heads,
                      write_state=cache.write)
-        mid = ctx.ws.buf("mix_core", T, N, act)
         ops.wkv_finish(raw, g, self.norm_weight, mid, heads=self.num_heads, eps=self.norm_eps)
         ops.linear(mid, self.out_weight, None, out=out_accum, accumulate=accumulate)
 

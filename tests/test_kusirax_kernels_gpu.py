@@ -292,6 +292,43 @@ def test_recurrence_in_unequal_portions_and_batches(ops, dtype, Hr, n, R, D):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hr,n,R,D", [(3, 16, 5, 64), (2, 64, 16, 96), (1, 40, 3, 64), (5, 8, 2, 24), (1, 1, 1, 8), (2, 96, 70, 32),
+                                      (1, 128, 64, 16)])
+def test_single_tokens_in_one_launch_leave_the_same_state(ops, dtype, Hr, n, R, D):
+    """Five requests, a prompt portion each through decay, scan and finish, then twelve steps of single tokens through the
+    single-launch kernel: its outputs equal what the three kernels give for the same tokens (rounding: the sums over the
+    state's rows meet in another grouping), and the states and kept rows are the same bits."""
+    assert ops.wkv_step_ok(n, R)
+    lens, steps, eps = [9, 1, 20, 3, 16], 12, 1e-5
+    N, B = Hr * n, 5
+    slots = [4, 0, 2, 1, 3]
+    state_a = torch.zeros(5, N * n + D, device=DEV)
+    full, ctx = _wkv_case(lens, Hr, n, R, D, dtype, seed=n + R, slots=slots)
+    z = rnd(sum(lens), N, seed=9, dtype=dtype)
+    weight = rnd(N, seed=10) * 0.3 + 1.0
+    dec = torch.empty(sum(lens), N, device=DEV)
+    raw = torch.empty(sum(lens), N, device=DEV)
+    ops.wkv_decay(full["low"], full["w2"], full["w0"], dec)
+    ops.wkv_scan(full["r"], full["k"], full["v"], dec, full["u"], full["h"], state_a, N * n, ctx, raw, heads=Hr)
+    state_b = state_a.clone()
+    for step in range(steps):
+        t, ctx1 = _wkv_case([1] * B, Hr, n, R, D, dtype, seed=100 + step, slots=slots)
+        ctx1.decode_only = True
+        z1 = rnd(B, N, seed=200 + step, dtype=dtype)
+        dec1, raw1 = torch.empty(B, N, device=DEV), torch.empty(B, N, device=DEV)
+        want = torch.empty(B, N, device=DEV, dtype=dtype)
+        ops.wkv_decay(t["low"], full["w2"], full["w0"], dec1)
+        ops.wkv_scan(t["r"], t["k"], t["v"], dec1, full["u"], t["h"], state_a, N * n, ctx1, raw1, heads=Hr)
+        ops.wkv_finish(raw1, z1, weight, want, heads=Hr, eps=eps)
+        got = torch.empty(B, N, device=DEV, dtype=dtype)
+        ops.wkv_step(t["r"], t["k"], t["v"], t["low"], full["w2"], full["w0"], full["u"], z1, weight, t["h"], state_b, N * n, ctx1,
+                     got, heads=Hr, eps=eps)
+        ops.check_device_errors()
+        assert (got.double() - want.double()).abs().max() < _tol(dtype) * max(1.0, want.double().abs().max().item()), step
+        assert torch.equal(state_a, state_b), step
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_token_shift_reads_the_row_before_also_across_steps(ops, dtype):
     D, NS = 40, 5
     mu = torch.rand(NS, D, generator=torch.Generator().manual_seed(1)).to(DEV)
