@@ -23,7 +23,6 @@
 namespace {
 
 constexpr int WKV_CH = 16;          // tokens per chunk of the scan
-constexpr int WKV_COLS = 32;        // columns of the state a CTA takes
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -112,25 +111,26 @@ struct WkvArgs {
     int Hr, n, D, write_state;
 };
 
-// grid (requests, heads, ceil(n / 32)); block (32, G), G = ceil(n / WR).  o [T][Hr*n] float.  The next chunk's inputs
+// grid (requests, heads, ceil(n / COLS)); block (COLS, G), G = ceil(n / WR).  o [T][Hr*n] float.  COLS, the columns of the
+// state a CTA takes, is 32, or 16 when that is what fills the SMs (few requests and heads).  The next chunk's inputs
 // are fetched into registers while the current chunk is walked, so the walk never waits for global memory.
-template <typename T, int WR>
-__global__ void __launch_bounds__(1024)
+template <typename T, int WR, int COLS>
+__global__ void __launch_bounds__(COLS * 32)
 wkv_scan_kernel(const T* r, const T* k, const T* v, const float* w, const T* h, float* __restrict__ o, WkvArgs a) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int PF = WKV_CH * WR / 32;      // elements of r (and of k, of w) a thread fetches per chunk
+    constexpr int PF = WKV_CH * WR / COLS;      // elements of r (and of k, of w) a thread fetches per chunk
     constexpr int PFV = 2;                    // elements of v a thread fetches ahead (WKV_CH / G of them; with fewer than 8
                                               // row groups, i.e. tiny heads, v is staged directly instead)
     const int n = a.n, G = blockDim.y, np = G * WR;    // rows padded to a multiple of WR: the padding has r = k = 0, w = 1
     float* rs = sm;                           // [CH][np]
     float* ks = rs + WKV_CH * np;             // [CH][np]
     float* ws = ks + WKV_CH * np;             // [CH][np]
-    float* vs = ws + WKV_CH * np;             // [CH][32]
-    float* os = vs + WKV_CH * WKV_COLS;       // [G][CH][32]
+    float* vs = ws + WKV_CH * np;             // [CH][COLS]
+    float* os = vs + WKV_CH * COLS;       // [G][CH][COLS]
     pdl_wait();
     pdl_launch();
-    const int seq = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * WKV_COLS;
-    const int lane = threadIdx.x, g = threadIdx.y, tid = g * 32 + lane, nthreads = G * 32;
+    const int seq = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * COLS;
+    const int lane = threadIdx.x, g = threadIdx.y, tid = g * COLS + lane, nthreads = G * COLS;
     const int t0 = a.cu_q[seq], t1 = a.cu_q[seq + 1];
     if (t1 <= t0) return;
     const int slot = a.slots[seq];
@@ -158,7 +158,7 @@ wkv_scan_kernel(const T* r, const T* k, const T* v, const float* w, const T* h, 
         e_c[x] = idx / np;
         e_i[x] = idx % np;
     }
-    const int vcount = (WKV_CH * WKV_COLS + nthreads - 1) / nthreads;
+    const int vcount = (WKV_CH * COLS + nthreads - 1) / nthreads;
     const bool v_ahead = vcount <= PFV;
     float pr[PF], pk[PF], pw[PF], pv[PFV];
     auto fetch = [&](int c0) {
@@ -178,8 +178,8 @@ wkv_scan_kernel(const T* r, const T* k, const T* v, const float* w, const T* h, 
         for (int x = 0; x < PFV; ++x) {
             pv[x] = 0.f;
             if (v_ahead && x < vcount) {
-                const int idx = tid + x * nthreads, c = idx / WKV_COLS, d = idx % WKV_COLS;
-                if (idx < WKV_CH * WKV_COLS && c < nc && j0 + d < n)
+                const int idx = tid + x * nthreads, c = idx / COLS, d = idx % COLS;
+                if (idx < WKV_CH * COLS && c < nc && j0 + d < n)
                     pv[x] = to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)hd * n + j0 + d]);
             }
         }
@@ -199,18 +199,18 @@ wkv_scan_kernel(const T* r, const T* k, const T* v, const float* w, const T* h, 
 #pragma unroll
             for (int x = 0; x < PFV; ++x) {
                 const int idx = tid + x * nthreads;
-                if (x < vcount && idx < WKV_CH * WKV_COLS) vs[idx] = pv[x];
+                if (x < vcount && idx < WKV_CH * COLS) vs[idx] = pv[x];
             }
         } else {
-            for (int idx = tid; idx < WKV_CH * WKV_COLS; idx += nthreads) {
-                const int c = idx / WKV_COLS, d = idx % WKV_COLS;
+            for (int idx = tid; idx < WKV_CH * COLS; idx += nthreads) {
+                const int c = idx / COLS, d = idx % COLS;
                 vs[idx] = (c < nc && j0 + d < n) ? to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)hd * n + j0 + d]) : 0.f;
             }
         }
         __syncthreads();
         if (c0 + WKV_CH < t1) fetch(c0 + WKV_CH);
         for (int c = 0; c < nc; ++c) {
-            const float vj = vs[c * WKV_COLS + lane];
+            const float vj = vs[c * COLS + lane];
             const float* rr = rs + c * np + g * WR;
             const float* kk = ks + c * np + g * WR;
             const float* ww = ws + c * np + g * WR;
@@ -221,14 +221,14 @@ wkv_scan_kernel(const T* r, const T* k, const T* v, const float* w, const T* h, 
                 acc = fmaf(rr[i], fmaf(uu[i], kv, s[i]), acc);
                 s[i] = fmaf(ww[i], s[i], kv);
             }
-            os[(g * WKV_CH + c) * WKV_COLS + lane] = acc;
+            os[(g * WKV_CH + c) * COLS + lane] = acc;
         }
         __syncthreads();
-        for (int idx = tid; idx < nc * WKV_COLS; idx += nthreads) {       // the row groups meet in group order
-            const int c = idx / WKV_COLS, d = idx % WKV_COLS;
+        for (int idx = tid; idx < nc * COLS; idx += nthreads) {       // the row groups meet in group order
+            const int c = idx / COLS, d = idx % COLS;
             if (j0 + d >= n) continue;
-            float acc = os[c * WKV_COLS + d];
-            for (int gg = 1; gg < G; ++gg) acc += os[(gg * WKV_CH + c) * WKV_COLS + d];
+            float acc = os[c * COLS + d];
+            for (int gg = 1; gg < G; ++gg) acc += os[(gg * WKV_CH + c) * COLS + d];
             o[(size_t)(c0 + c) * a.o_stride + (size_t)hd * n + j0 + d] = acc;
         }
     }
@@ -399,28 +399,44 @@ MLLM_EXPORT int mllm_wkv_decay(const void* low, long long l_stride, const void* 
 }
 
 // r, k, v [T, Hr*n] in `dtype`; w [T, Hr*n] float (the decays); u [Hr*n] float; h [T, D] (its last row of every request is
-// kept); state [slots][state_stride] float with S at 0 and the kept row at prev_off; o [T, Hr*n] float.
+// kept); state [slots][state_stride] float with S at 0 and the kept row at prev_off; o [T, Hr*n] float.  want_cols: the
+// columns of a state per CTA, 16 or 32, or 0 for the rule below (outputs and states are the same bits either way).
 MLLM_EXPORT int mllm_wkv_scan(const void* r, long long r_stride, const void* k, long long k_stride, const void* v,
                               long long v_stride, const float* w, long long w_stride, const float* u, const void* h,
                               long long h_stride, float* state, long long state_stride, long long prev_off, const int* cu_q,
                               const int* slots, float* o, long long o_stride, int S, int Hr, int n, int D, int write_state,
-                              int dtype, cudaStream_t stream) {
+                              int want_cols, int dtype, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (Hr <= 0 || n <= 0 || n > 256) return mllm_fail(1, "wkv_scan: %d heads of %d", Hr, n);
     if (Hr > 65535) return mllm_fail(1, "wkv_scan: grid of %d x %d", S, Hr);
     const int WR = n <= 64 ? 2 : (n <= 128 ? 4 : 8);
     const int G = (n + WR - 1) / WR, np = G * WR;
-    const size_t smem = sizeof(float) * ((size_t)3 * WKV_CH * np + WKV_CH * WKV_COLS + (size_t)G * WKV_CH * WKV_COLS);
+    // 32 columns of a state per CTA; 16 where the narrower tiles still find an SM each (every CTA is one chain of dependent
+    // token steps: more, narrower CTAs shorten the step's critical path as long as they all run at once; measured at 2 x 1,024
+    // tokens: 12 heads of 64: 209 -> 178 us; 32 heads of 64, whose 256 narrow CTAs exceed the SMs: 220 -> 240 us)
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        MLLM_CUDA(cudaGetDevice(&dev));
+        MLLM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (want_cols != 0 && want_cols != 16 && want_cols != 32) return mllm_fail(1, "wkv_scan: %d columns per CTA (16, 32, or 0 for the rule)", want_cols);
+    const int cols = want_cols ? want_cols : ((n > 16 && (long long)S * Hr * ((n + 15) / 16) <= sms) ? 16 : 32);
+    const size_t smem = sizeof(float) * ((size_t)3 * WKV_CH * np + WKV_CH * cols + (size_t)G * WKV_CH * cols);
     if (smem > 200 * 1024) return mllm_fail(1, "wkv_scan: heads of %d need %zu bytes of shared memory", n, smem);
     WkvArgs a{cu_q, slots, u, state, state_stride, prev_off, r_stride, k_stride, v_stride, w_stride, o_stride, h_stride,
               Hr, n, D, write_state};
-    const dim3 grid(S, Hr, (n + WKV_COLS - 1) / WKV_COLS), block(32, G);
-#define MLLM_WKV(TT, WRR)                                                                                                \
+    const dim3 grid(S, Hr, (n + cols - 1) / cols), block(cols, G);
+#define MLLM_WKV_C(TT, WRR, CC)                                                                                          \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
-            MLLM_CUDA(cudaFuncSetAttribute(wkv_scan_kernel<TT, WRR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        MLLM_CUDA(mllm_launch(wkv_scan_kernel<TT, WRR>, grid, block, smem, stream, true, (const TT*)r, (const TT*)k,    \
+            MLLM_CUDA(cudaFuncSetAttribute(wkv_scan_kernel<TT, WRR, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MLLM_CUDA(mllm_launch(wkv_scan_kernel<TT, WRR, CC>, grid, block, smem, stream, true, (const TT*)r, (const TT*)k, \
                               (const TT*)v, w, (const TT*)h, o, a));                                                     \
+    } while (0)
+#define MLLM_WKV(TT, WRR)                                                                                                \
+    do {                                                                                                                 \
+        if (cols == 16) MLLM_WKV_C(TT, WRR, 16); else MLLM_WKV_C(TT, WRR, 32);                                           \
     } while (0)
     if (dtype == MLLM_F32) {
         if (WR == 2) MLLM_WKV(float, 2); else if (WR == 4) MLLM_WKV(float, 4); else MLLM_WKV(float, 8);
@@ -430,6 +446,7 @@ MLLM_EXPORT int mllm_wkv_scan(const void* r, long long r_stride, const void* k, 
         return mllm_fail(1, "wkv_scan: unknown dtype code %d", dtype);
     }
 #undef MLLM_WKV
+#undef MLLM_WKV_C
     return 0;
 }
 

@@ -113,7 +113,7 @@ def _signatures(lib):
                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_wkv_decay": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_wkv_scan": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p,
-                          c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                          c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_wkv_finish": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int,
                             c_void_p],
         "mllm_wkv_max_dim": [],
@@ -1145,11 +1145,12 @@ def wkv_decay(low, w2, w0, out) -> None:
           T, N, R, _dt(low), _stream())
 
 
-def wkv_scan(r, k, v, w, u, h, state, prev_off: int, ctx, out, *, heads: int, write_state: bool = True) -> None:
+def wkv_scan(r, k, v, w, u, h, state, prev_off: int, ctx, out, *, heads: int, write_state: bool = True, cols: int = 0) -> None:
     """The recurrence of csrc/wkv.cu over the step's tokens, request by request: o = (S + diag(u) k v^T)^T r;
     S <- diag(w) S + k v^T.  r, k, v [T, heads * n] in one dtype; w (the decays, ``wkv_decay``) float32 [T, heads * n];
     u float32 [heads * n]; state float32 [slots, row] with S [heads, n, n] at column 0 and the last row of h
-    [T, D] of every request kept at column ``prev_off``; out float32 [T, heads * n]."""
+    [T, D] of every request kept at column ``prev_off``; out float32 [T, heads * n].  ``cols``: columns of a state per CTA,
+    16 or 32 (0: the library's rule by the size of the grid; the same bits either way)."""
     _cuda("r", r, contiguous=False)
     for name, t in (("k", k), ("v", v), ("h", h)):
         _cuda(name, t, r.dtype, contiguous=False)
@@ -1168,7 +1169,7 @@ def wkv_scan(r, k, v, w, u, h, state, prev_off: int, ctx, out, *, heads: int, wr
     _call("mllm_wkv_scan", r.data_ptr(), _rows("r", r), k.data_ptr(), _rows("k", k), v.data_ptr(), _rows("v", v),
           w.data_ptr(), _rows("w", w), u.data_ptr(), h.data_ptr(), _rows("h", h), state.data_ptr(), state.stride(0),
           int(prev_off), ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), _rows("out", out), ctx.S,
-          int(heads), n, D, int(write_state), _dt(r), _stream())
+          int(heads), n, D, int(write_state), int(cols), _dt(r), _stream())
 
 
 def wkv_step_ok(n: int, rank: int) -> bool:

@@ -256,7 +256,7 @@ def test_recurrence_in_unequal_portions_and_batches(ops, dtype, Hr, n, R, D):
         out = torch.empty(rows.numel(), N, device=DEV)
         dec = torch.empty(rows.numel(), N, device=DEV)
         ops.wkv_decay(t["low"], full["w2"], full["w0"], dec)
-        ops.wkv_scan(t["r"], t["k"], t["v"], dec, full["u"], t["h"], state, N * n, ctx, out, heads=Hr)
+        ops.wkv_scan(t["r"], t["k"], t["v"], dec, full["u"], t["h"], state, N * n, ctx, out, heads=Hr, cols=(0, 32, 16, 0)[len(live) % 4])
         ops.check_device_errors()
         o = 0
         for i in live:
@@ -279,8 +279,14 @@ def test_recurrence_in_unequal_portions_and_batches(ops, dtype, Hr, n, R, D):
         dec_all = torch.empty(L, N, device=DEV)
         ops.wkv_decay(full["low"][sl], full["w2"], full["w0"], dec_all)
         assert (dec_all.double().cpu() - dec).abs().max() < 3e-6         # the decays themselves, in (0, 1)
-        ops.wkv_scan(full["r"][sl], full["k"][sl], full["v"][sl], dec_all, full["u"], full["h"][sl], one, N * n, ctx, out, heads=Hr)
+        ops.wkv_scan(full["r"][sl], full["k"][sl], full["v"][sl], dec_all, full["u"], full["h"][sl], one, N * n, ctx, out, heads=Hr,
+                     cols=16)
         assert torch.equal(one[slots[i]], state[slots[i]])       # the same bits however the tokens were cut
+        # 32 or 16 columns of a state per CTA: the same outputs and the same state, bit for bit
+        other, out32 = torch.zeros(4, N * n + D, device=DEV), torch.empty(L, N, device=DEV)
+        ops.wkv_scan(full["r"][sl], full["k"][sl], full["v"][sl], dec_all, full["u"], full["h"][sl], other, N * n, ctx, out32, heads=Hr,
+                     cols=32)
+        assert torch.equal(out32, out) and torch.equal(other[slots[i]], one[slots[i]])
     assert torch.all(state[1] == 9.0)
     # the channel that never forgets still holds the first token's k v^T; the one that forgets at once only the last token's
     if N == 1:
